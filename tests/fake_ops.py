@@ -139,3 +139,133 @@ def sample(logits, temperature, top_k, top_p, u, out):
         c = torch.cumsum(e, 0)
         idx = int(torch.searchsorted(c, torch.tensor(float(u[r]) * float(c[-1]), dtype=torch.float64), right=True))
         out[r] = min(idx, z.numel() - 1)
+
+
+# ---- the kernels of the layer norm, the general attention, the recurrent mixers and the PolyNorm activation ----
+
+
+def layernorm(x, delta, weight, eps, out, rows=None, status=None):
+    idx = torch.arange(x.shape[0]) if rows is None else rows.long()
+    v = x[idx]
+    if delta is not None:
+        v = v + delta[idx].float()
+        x[idx] = v
+    dev = v - v.mean(dim=-1, keepdim=True)
+    out.copy_((weight * dev * torch.rsqrt((dev * dev).mean(dim=-1, keepdim=True) + eps)).to(out.dtype))
+
+
+def polynorm(z, coefficients, eps, out):
+    a, b, c, e = [float(v) for v in coefficients]
+    zf = z.float()
+    n = lambda y: y * torch.rsqrt((y * y).mean(dim=-1, keepdim=True) + eps)
+    out.copy_((a * n(zf) + b * n(zf * zf) + c * n(zf * zf * zf) + e).to(out.dtype))
+
+
+def head_norm_gate(o, y, gate_col, weight, weight_per_channel, eps, act, out, out_col, out_scale, heads, v_dim):
+    T = o.shape[0]
+    oh = o.view(T, heads, v_dim)
+    n = oh * torch.rsqrt((oh * oh).mean(dim=-1, keepdim=True) + eps)
+    w = weight.view(heads, v_dim) if weight_per_channel else weight.view(1, v_dim)
+    g = y[:, gate_col:gate_col + heads * v_dim].float().view(T, heads, v_dim)
+    g = g * torch.sigmoid(g) if act == 0 else torch.sigmoid(g)
+    out[:, out_col:out_col + heads * v_dim] = (out_scale * n * w * g).reshape(T, heads * v_dim).to(out.dtype)
+
+
+def _sequences(cu_q, rows):
+    cu = cu_q.tolist()
+    return [(int(rows[i]), cu[i], cu[i + 1]) for i in range(len(cu) - 1) if cu[i + 1] > cu[i]]
+
+
+def gla_scan(y, q_col, k_col, v_col, a_col, a2, a2_bias, inv_tau, q_scale, state, cu_q, rows, o, heads, dim, v_dim, status=None):
+    rank = a2.shape[1]
+    yf = y.float()
+    z = yf[:, a_col:a_col + rank] @ a2.t() + a2_bias
+    alpha = torch.exp(torch.nn.functional.logsigmoid(z) * inv_tau).view(-1, heads, dim)
+    q = yf[:, q_col:q_col + heads * dim].view(-1, heads, dim) * q_scale
+    k = yf[:, k_col:k_col + heads * dim].view(-1, heads, dim)
+    v = yf[:, v_col:v_col + heads * v_dim].view(-1, heads, v_dim)
+    for row, a, b in _sequences(cu_q, rows):
+        S = state[row].clone()
+        for t in range(a, b):
+            S = alpha[t][:, :, None] * S + k[t][:, :, None] * v[t][:, None, :]
+            o[t] = torch.einsum("hdv,hd->hv", S, q[t]).reshape(-1)
+        state[row] = S
+
+
+def delta_scan(y, r_col, k_col, v_col, a_col, w1_col, w2, w0, a_bias, decay_rate, key_eps, state, cu_q, rows, o, heads, dim,
+               status=None):
+    rank = w2.shape[1]
+    yf = y.float()
+    n = heads * dim
+    w = torch.exp(-decay_rate * torch.sigmoid(torch.tanh(yf[:, w1_col:w1_col + rank]) @ w2.t() + w0)).view(-1, heads, dim)
+    a = torch.sigmoid(yf[:, a_col:a_col + n] + a_bias).view(-1, heads, dim)
+    r = yf[:, r_col:r_col + n].view(-1, heads, dim)
+    k = yf[:, k_col:k_col + n].view(-1, heads, dim)
+    v = yf[:, v_col:v_col + n].view(-1, heads, dim)
+    u = k / torch.sqrt((k * k).sum(dim=-1, keepdim=True) + key_eps)
+    for row, lo, hi in _sequences(cu_q, rows):
+        S = state[row].clone()
+        for t in range(lo, hi):
+            uS = torch.einsum("hd,hdv->hv", u[t], S)
+            S = w[t][:, :, None] * S - (a[t] * u[t])[:, :, None] * uS[:, None, :] + k[t][:, :, None] * v[t][:, None, :]
+            o[t] = torch.einsum("hdv,hd->hv", S, r[t]).reshape(-1)
+        state[row] = S
+
+
+def attention_prepare(y, q_col, k_col, v_col, positions, token_seq, frequencies, norm_eps, k_cache, v_cache, block_table,
+                      heads, kv_heads, dim, v_dim, store, status=None):
+    T = y.shape[0]
+    page_size = k_cache.shape[2]
+    live = token_seq >= 0
+
+    def turn(x):                                   # x [T, n, dim] float
+        if frequencies is not None and frequencies.numel():
+            half = frequencies.numel()
+            ang = positions.float()[:, None] * frequencies.float()[None, :]
+            c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+            a, b = x[..., :half].clone(), x[..., half:2 * half].clone()
+            x[..., :half] = a * c - b * s
+            x[..., half:2 * half] = b * c + a * s
+        if norm_eps >= 0:
+            x = x * torch.rsqrt((x * x).mean(dim=-1, keepdim=True) + norm_eps)
+        return x
+
+    q = turn(y[:, q_col:q_col + heads * dim].float().view(T, heads, dim).clone())
+    y[:, q_col:q_col + heads * dim] = q.reshape(T, heads * dim).to(y.dtype)
+    if not store:
+        return
+    k = turn(y[:, k_col:k_col + kv_heads * dim].float().view(T, kv_heads, dim).clone())
+    v = y[:, v_col:v_col + kv_heads * v_dim].view(T, kv_heads, v_dim)
+    for t in range(T):
+        if not bool(live[t]):
+            continue
+        p = int(positions[t])
+        page = int(block_table[int(token_seq[t]), p // page_size])
+        assert page >= 0, "a key is stored into a page that is not held"
+        k_cache[page, :, p % page_size, :] = k[t].to(k_cache.dtype)
+        v_cache[page, :, p % page_size, :] = v[t].to(v_cache.dtype)
+
+
+def attention_general(y, q_col, out, out_col, out_scale, k_cache, v_cache, positions, token_seq, block_table, heads, kv_heads,
+                      dim, v_dim, window, chunk, scale, status=None):
+    T = y.shape[0]
+    page_size = k_cache.shape[2]
+    g = heads // kv_heads
+    q = y[:, q_col:q_col + heads * dim].float().view(T, heads, dim)
+    for t in range(T):
+        s = int(token_seq[t])
+        if s < 0:
+            out[t, out_col:out_col + heads * v_dim] = 0
+            continue
+        p = int(positions[t])
+        first = max(0, p - window + 1) if window > 0 else 0
+        if chunk > 0:
+            first = max(first, (p // chunk) * chunk)
+        js = torch.arange(first, p + 1)
+        pages = block_table[s, (js // page_size)].long()
+        assert bool((pages >= 0).all()), "attention reads a page that is not held"
+        keys = k_cache[pages, :, js % page_size, :].float()
+        vals = v_cache[pages, :, js % page_size, :].float()
+        for h in range(heads):
+            pr = torch.softmax((keys[:, h // g, :] @ q[t, h]) * scale, dim=0)
+            out[t, out_col + h * v_dim:out_col + (h + 1) * v_dim] = (out_scale * (pr @ vals[:, h // g, :])).to(out.dtype)

@@ -1,4 +1,5 @@
 from .base import ConfigError, KeyReader, ModelConfig
 from .qwen2 import Qwen2Config
+from .sisetar import SisetarConfig
 from .registry import (Architecture, config_from_dict, get_architecture, known_architectures, load_config,
                        register_architecture, unregister_architecture)

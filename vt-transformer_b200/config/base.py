@@ -115,7 +115,12 @@ def read_config_json(folder: str) -> Dict[str, Any]:
 
 
 def architecture_name(data: Dict[str, Any], where: str = "config.json") -> str:
+    """The registry key of a config.json: ``architectures[0]``, or the string under ``architecture`` in files
+    that name their design that way."""
     archs = data.get("architectures")
+    if archs is None and isinstance(data.get("architecture"), str) and data["architecture"]:
+        return data["architecture"]
     if not isinstance(archs, list) or not archs or not isinstance(archs[0], str):
-        raise ConfigError(f"{where}: key 'architectures' must be a list that names the model class")
+        raise ConfigError(f"{where}: key 'architectures' must be a list that names the model class "
+                          f"(or 'architecture' a string)")
     return archs[0]

@@ -39,17 +39,23 @@ class DecoderModel:
                 continue
             if run.cache is None:
                 raise ValueError(f"run {n}: block {run.block} keeps a cache but the run names no slot")
-            if run.writes:
-                if run.cache in slots:
-                    raise ValueError(f"run {n}: cache slot {run.cache} is written by an earlier run already")
-                slots[run.cache] = need
-            else:
-                if run.cache not in slots:
-                    raise ValueError(f"run {n} reads cache slot {run.cache} before any run wrote it")
-                have = slots[run.cache]
-                if type(have) is not type(need) or getattr(have, "kv_heads", None) != getattr(need, "kv_heads", None) \
-                        or getattr(have, "head_dim", None) != getattr(need, "head_dim", None):
-                    raise ValueError(f"run {n}: cache slot {run.cache} has another layout than block {run.block} reads")
+            # a mixer that keeps several things names a spec for each, and the run a slot for each
+            needs = tuple(need) if isinstance(need, (tuple, list)) else (need,)
+            named = tuple(run.cache) if isinstance(run.cache, (tuple, list)) else (run.cache,)
+            if len(needs) != len(named):
+                raise ValueError(f"run {n}: block {run.block} keeps {len(needs)} caches but the run names {len(named)} slots")
+            for slot, spec in zip(named, needs):
+                if run.writes:
+                    if slot in slots:
+                        raise ValueError(f"run {n}: cache slot {slot} is written by an earlier run already")
+                    slots[slot] = spec
+                else:
+                    if slot not in slots:
+                        raise ValueError(f"run {n} reads cache slot {slot} before any run wrote it")
+                    have = slots[slot]
+                    if type(have) is not type(spec) or getattr(have, "kv_heads", None) != getattr(spec, "kv_heads", None) \
+                            or getattr(have, "head_dim", None) != getattr(spec, "head_dim", None):
+                        raise ValueError(f"run {n}: cache slot {slot} has another layout than block {run.block} reads")
         self._slots = slots
 
     def cache_slots(self) -> Dict[int, object]:
@@ -94,15 +100,22 @@ class DecoderModel:
         return n + self.head.weight_bytes() + self.embedding.step_bytes(n_tokens)
 
     # ---- forward -------------------------------------------------------------------
+    @staticmethod
+    def _view(views: Dict[int, CacheView], slot, writes: bool) -> Optional[CacheView]:
+        view = views.get(slot)
+        if view is not None and view.writes != writes:
+            view = CacheView(**{**view.__dict__, "writes": writes})
+        return view
+
     def forward(self, ctx, views: Dict[int, CacheView]) -> torch.Tensor:
         """Runs the step's tokens and returns float32 logits [wanted rows, vocab].
         ``views[slot]`` is the cache view of a slot for this step."""
         stream = ResidualStream(self.embedding.forward(ctx), status=ctx.status)
         for run in self.spec.order:
-            view: Optional[CacheView] = None
-            if run.cache is not None and run.cache in views:
-                view = views[run.cache]
-                if view.writes != run.writes:
-                    view = CacheView(**{**view.__dict__, "writes": run.writes})
+            view = None
+            if isinstance(run.cache, (tuple, list)):
+                view = tuple(self._view(views, slot, run.writes) for slot in run.cache)
+            elif run.cache is not None:
+                view = self._view(views, run.cache, run.writes)
             self.blocks[run.block].forward(stream, ctx, view)
         return self.head.forward(stream, ctx)

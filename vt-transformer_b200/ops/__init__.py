@@ -95,6 +95,84 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
     return out
 
 
+def layernorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, delta=None,
+              rows: Optional[torch.Tensor] = None, status=None) -> torch.Tensor:
+    """out = weight * (v - mean(v)) * rsqrt(var(v) + eps) over the rows ``rows`` (all) of v = x + delta, which is
+    written back to x; var is the mean of the squared deviations.  ``delta`` as for ``rmsnorm``."""
+    if isinstance(delta, SplitSum):
+        delta = delta.shares
+    backend().layernorm(x, delta, weight, float(eps), out, rows, status)
+    return out
+
+
+def polynorm(z: torch.Tensor, coefficients: torch.Tensor, eps: float, out: torch.Tensor) -> torch.Tensor:
+    """out = a N(z) + b N(z^2) + c N(z^3) + e row by row, N(y) = y / sqrt(mean(y^2) + eps), (a, b, c, e) the four
+    float32 numbers of ``coefficients``; powers and means in 32-bit.  ``out`` may be ``z``."""
+    backend().polynorm(z, coefficients, float(eps), out)
+    return out
+
+
+def head_norm_gate(o: torch.Tensor, y: torch.Tensor, gate_col: int, weight: torch.Tensor, weight_per_channel: bool,
+                   eps: float, act: str, out: torch.Tensor, out_col: int, out_scale: float, heads: int, v_dim: int) -> torch.Tensor:
+    """out[t, out_col + h * v_dim + i] = out_scale * o[t, h, i] / sqrt(mean_i(o[t, h, :]^2) + eps) * w * act(gate)
+    for the 32-bit o [T, heads * v_dim] of a recurrent mixer; gate = y[t, gate_col + h * v_dim + i]; w = weight[i]
+    (a weight [v_dim] shared by the heads) or, with ``weight_per_channel``, weight[h * v_dim + i]; ``act`` is
+    "silu" or "sigmoid".  32-bit until the one rounding into ``out``."""
+    backend().head_norm_gate(o, y, int(gate_col), weight, bool(weight_per_channel), float(eps), _GATE_ACTS[act], out,
+                             int(out_col), float(out_scale), int(heads), int(v_dim))
+    return out
+
+
+_GATE_ACTS = {"silu": 0, "sigmoid": 1}
+
+
+def gla_scan(y, q_col: int, k_col: int, v_col: int, a_col: int, a2: torch.Tensor, a2_bias: torch.Tensor, inv_tau: float,
+             q_scale: float, state: torch.Tensor, ctx, o: torch.Tensor, heads: int, dim: int, v_dim: int, status=None):
+    """Gated linear attention over the step's tokens, sequence by sequence and head by head, in the order of the
+    tokens: S <- diag(alpha_t) S + k_t v_t^T, o_t = S^T (q_scale * q_t), with log alpha = log sigmoid(z) * inv_tau and
+    z = a2 (low-rank input at ``a_col``) + a2_bias.  q, k, v and the low-rank input are columns of ``y``; ``state``
+    [request rows, heads, dim, v_dim] (float32) is read at the step's ``ctx.rows`` and left as after the last token;
+    ``o`` [T, heads * v_dim] is float32.  Decay, state and sums are 32-bit."""
+    backend().gla_scan(y, int(q_col), int(k_col), int(v_col), int(a_col), a2, a2_bias, float(inv_tau), float(q_scale),
+                       state, ctx.cu_q, ctx.rows, o, int(heads), int(dim), int(v_dim), status)
+    return o
+
+
+def delta_scan(y, r_col: int, k_col: int, v_col: int, a_col: int, w1_col: int, w2: torch.Tensor, w0: torch.Tensor,
+               a_bias: torch.Tensor, decay_rate: float, key_eps: float, state: torch.Tensor, ctx, o: torch.Tensor,
+               heads: int, dim: int, status=None):
+    """The generalized delta rule over the step's tokens, sequence by sequence and head by head:
+    S <- diag(w_t) S - (a_t * u_t)(u_t^T S) + k_t v_t^T, o_t = S^T r_t, with u = k / sqrt(sum(k^2) + key_eps),
+    w = exp(-decay_rate * sigmoid(w2 tanh(low-rank input at ``w1_col``) + w0)) and a = sigmoid(y at ``a_col`` + a_bias).
+    ``state`` [request rows, heads, dim, dim] float32; ``o`` [T, heads * dim] float32."""
+    backend().delta_scan(y, int(r_col), int(k_col), int(v_col), int(a_col), int(w1_col), w2, w0, a_bias, float(decay_rate),
+                         float(key_eps), state, ctx.cu_q, ctx.rows, o, int(heads), int(dim), status)
+    return o
+
+
+def attention_prepare(y, q_col: int, k_col: int, v_col: int, ctx, frequencies, norm_eps, k_cache, v_cache, block_table,
+                      heads: int, kv_heads: int, dim: int, v_dim: int, store: bool = True, status=None) -> None:
+    """What the general attention does to a step's q, k and v (columns of ``y``) before its keys are walked: the
+    first 2 * len(frequencies) dimensions of every head of q and k are rotated, pairs (i, i + len), by
+    position * frequencies[i] (a 32-bit product; ``frequencies`` None: no rotation); then, with ``norm_eps`` not None,
+    every head of q and k is divided by sqrt(mean(.^2) + norm_eps); q is written back into ``y``, k and v go into
+    their pages ([pages, kv_heads, page_size, dim] and [..., v_dim]) if ``store``."""
+    backend().attention_prepare(y, int(q_col), int(k_col), int(v_col), ctx.positions, ctx.token_seq, frequencies,
+                                -1.0 if norm_eps is None else float(norm_eps), k_cache, v_cache, block_table, int(heads),
+                                int(kv_heads), int(dim), int(v_dim), bool(store), status)
+
+
+def attention_general(y, q_col: int, out, out_col: int, out_scale: float, k_cache, v_cache, ctx, block_table, heads: int,
+                      kv_heads: int, dim: int, v_dim: int, window, chunk, scale: float, status=None):
+    """out[t, out_col + h * v_dim + :] = out_scale * softmax(scale * q . k_j) v_j over the keys j that token t at
+    position p sees: j <= p, j > p - window (if a window is given) and j // chunk == p // chunk (if chunks are).
+    q is read at column ``q_col`` of ``y``; keys of size ``dim`` and values of size ``v_dim`` from their pages."""
+    backend().attention_general(y, int(q_col), out, int(out_col), float(out_scale), k_cache, v_cache, ctx.positions,
+                                ctx.token_seq, block_table, int(heads), int(kv_heads), int(dim), int(v_dim),
+                                int(window) if window else 0, int(chunk) if chunk else 0, float(scale), status)
+    return out
+
+
 def silu_mul(gu: torch.Tensor, out: torch.Tensor, interleave: int = 0) -> torch.Tensor:
     """out = silu(gate) * up.  ``interleave`` 0: gu = [gate | up]; 8: gate and up columns alternate in
     runs of 8 (``interleave_gate_up``)."""
@@ -506,5 +584,6 @@ def _counted(fn):
     return wrapper
 
 
-for _name in ("embedding", "logits_scale_cap", "rmsnorm", "silu_mul", "rope_store", "linear", "paged_attention", "argmax", "sample"):  # the others count where they launch
+for _name in ("embedding", "logits_scale_cap", "rmsnorm", "layernorm", "polynorm", "head_norm_gate", "gla_scan", "delta_scan",
+              "attention_prepare", "attention_general", "silu_mul", "rope_store", "linear", "paged_attention", "argmax", "sample"):  # the others count where they launch
     globals()[_name] = _counted(globals()[_name])

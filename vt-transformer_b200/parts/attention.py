@@ -6,9 +6,20 @@ import math
 import torch
 
 from .base import KVCacheSpec, Mixer, ParamSpec, build_part, register_part
+from .projected import ProjectedMixer
 
 
-@register_part("mixer", "attention")
+def _attention(spec, prefix, rt):
+    """The attention mixer for a spec: the kernels of ``PagedAttention`` take the whole head rotated from a table,
+    values as wide as keys and a causal or windowed mask; everything else runs ``GeneralAttention``."""
+    plain = (spec.v_dim in (None, spec.head_dim) and spec.qk_norm_eps is None and spec.chunk is None
+             and spec.position.kind != "rotary_computed")
+    return (PagedAttention if plain else GeneralAttention)(spec, prefix, rt)
+
+
+register_part("mixer", "attention", _attention)
+
+
 class PagedAttention(Mixer):
     """q, k, v = h Wq^T + bq, h Wk^T + bk, h Wv^T + bv (one product over the packed rows of
     the three matrices, which equals the three separate products of
@@ -87,3 +98,70 @@ class PagedAttention(Mixer):
         ops.rope_attention(qkv, o, self.position.table, cache.k, cache.v, ctx, cache.block_table, s.heads, s.kv_heads,
                            s.head_dim, s.window, self.scale, store=cache.writes, status=ctx.status)
         return ops.linear_to_stream(o, self.w_o, self.b_o, then=self.then)
+
+
+class GeneralAttention(ProjectedMixer):
+    """Grouped-query attention with the options that ``PagedAttention``'s kernels do not take: values of another size
+    than keys (``v_dim``), a rotation of the first dimensions of a head only, with the angle formed where it is used
+    (``rotary_computed``), q and k divided by their root mean square after the rotation (``qk_norm_eps``), and a mask
+    of chunks (``chunk``) beside or instead of the window.  One kernel rotates and norms q and k (32-bit) and stores
+    k and v into the pages; the attention kernel walks the visible keys of every (token, head) with a running maximum
+    and sum in 32-bit.  No biases."""
+
+    def __init__(self, spec, prefix, rt):
+        super().__init__(spec, prefix, rt)
+        if spec.qkv_bias or spec.out_bias:
+            raise ValueError("attention: biases are built for the plain attention only (rotation of the whole head, "
+                             "values as wide as keys, no norm of q and k, no chunks)")
+        if spec.position.kind not in ("rotary_computed", "none"):
+            raise ValueError(f"attention: position encoding '{spec.position.kind}' is not built beside the general options; "
+                             f"known: rotary_computed, none")
+        if spec.position.kind != "none" and (spec.position.dim % 2 or spec.position.dim > spec.head_dim):
+            raise ValueError(f"attention: the rotation covers {spec.position.dim} dimensions; it must be even and at most "
+                             f"the head's {spec.head_dim}")
+        self.position = build_part("position", spec.position, prefix, rt)
+        self.v_dim = spec.v_dim if spec.v_dim else spec.head_dim
+        self.scale = spec.scale if spec.scale is not None else 1.0 / math.sqrt(spec.head_dim)
+
+    def cache_spec(self):
+        s = self.spec
+        return KVCacheSpec(s.kv_heads, s.head_dim, s.window, v_dim=self.v_dim if self.v_dim != s.head_dim else None)
+
+    def param_specs(self):
+        s, p, x = self.spec, self.prefix, self.spec.weight_suffix
+        q, k, v, o = s.names
+        return {
+            f"{p}{q}{x}": ParamSpec((s.heads * s.head_dim, s.hidden)),
+            f"{p}{k}{x}": ParamSpec((s.kv_heads * s.head_dim, s.hidden)),
+            f"{p}{v}{x}": ParamSpec((s.kv_heads * self.v_dim, s.hidden)),
+            f"{p}{o}{x}": ParamSpec((s.hidden, s.heads * self.v_dim)),
+        }
+
+    def load(self, get) -> None:
+        s, p, rt, x = self.spec, self.prefix, self.rt, self.spec.weight_suffix
+        q, k, v, o = s.names
+        self._in = [rt.param(get(f"{p}{n}{x}")) for n in (q, k, v)]
+        self.w_o = rt.param(get(f"{p}{o}{x}"))
+        self.position.load(get)
+        self.pack()
+
+    def release_unpacked(self) -> None:
+        self._in = self.w_o = None
+
+    def in_matrices(self):
+        return list(self._in)
+
+    def out_matrix(self):
+        return self.w_o
+
+    def inner_size(self) -> int:
+        return self.spec.heads * self.v_dim
+
+    def core(self, y, cols, ctx, cache, out, out_col, out_scale) -> None:
+        s, ops = self.spec, self.rt.ops
+        freq = getattr(self.position, "frequencies", None)
+        k_pages, v_pages = cache.pages["k"], cache.pages["v"]
+        ops.attention_prepare(y, cols[0], cols[1], cols[2], ctx, freq, s.qk_norm_eps, k_pages, v_pages, cache.block_table,
+                              s.heads, s.kv_heads, s.head_dim, self.v_dim, store=cache.writes, status=ctx.status)
+        ops.attention_general(y, cols[0], out, out_col, out_scale, k_pages, v_pages, ctx, cache.block_table, s.heads,
+                              s.kv_heads, s.head_dim, self.v_dim, s.window, s.chunk, self.scale, status=ctx.status)

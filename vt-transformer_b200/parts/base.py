@@ -35,6 +35,15 @@ class ParamSpec:
     init: str = "normal"
     optional: bool = False
 
+    # A negative entry -k of ``shape`` is a size that the weights decide (a low-rank gate's rank, which no
+    # configuration names): any size is accepted there, and the random initialiser makes k.
+    def fits(self, shape) -> bool:
+        shape = tuple(shape)
+        return len(shape) == len(self.shape) and all(want < 0 or want == got for want, got in zip(self.shape, shape))
+
+    def made_shape(self) -> Tuple[int, ...]:
+        return tuple(abs(d) for d in self.shape)
+
 
 # ----------------------------------------------------------------------------- runtime
 
@@ -97,6 +106,7 @@ class KVCacheSpec:
     kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    v_dim: Optional[int] = None        # size of a value where it differs from a key's (None: head_dim)
 
 
 @dataclass(frozen=True)
@@ -144,7 +154,8 @@ def cache_layout(spec):
                     f"(parts.register_cache_kind adds one)")
 
 
-register_cache_kind(KVCacheSpec, lambda s: PagedLayout((("k", s.kv_heads, s.head_dim), ("v", s.kv_heads, s.head_dim)), s.window))
+register_cache_kind(KVCacheSpec, lambda s: PagedLayout((("k", s.kv_heads, s.head_dim),
+                                                        ("v", s.kv_heads, s.v_dim if s.v_dim else s.head_dim)), s.window))
 register_cache_kind(StateSpec, lambda s: StateLayout(tuple(s.shape), s.dtype))
 
 
@@ -230,6 +241,8 @@ class Mixer(Part):
     category = "mixer"
 
     def cache_spec(self):
+        """None, one cache spec, or a tuple of them for a mixer that keeps several things (keys and values in
+        pages beside a recurrent state): ``forward`` then gets a tuple of views in the same order."""
         return None
 
     def forward(self, h, ctx, cache):

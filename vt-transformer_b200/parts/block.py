@@ -13,10 +13,12 @@ class PreNormBlock(Block):
     def __init__(self, spec, prefix, rt):
         super().__init__(spec, prefix, rt)
         self.norm1 = build_part("norm", spec.norm1, prefix + spec.norm1_name, rt)
-        self.norm2 = build_part("norm", spec.norm2, prefix + spec.norm2_name, rt)
         self.mixer = build_part("mixer", spec.mixer, prefix + spec.mixer_prefix, rt)
-        self.ffn = build_part("feed_forward", spec.ffn, prefix + spec.ffn_prefix, rt)
-        self.parts = (self.norm1, self.mixer, self.norm2, self.ffn)
+        self.norm2 = self.ffn = None
+        if spec.ffn is not None:            # a layer without a feed-forward has the first sublayer only
+            self.norm2 = build_part("norm", spec.norm2, prefix + spec.norm2_name, rt)
+            self.ffn = build_part("feed_forward", spec.ffn, prefix + spec.ffn_prefix, rt)
+        self.parts = tuple(p for p in (self.norm1, self.mixer, self.norm2, self.ffn) if p is not None)
 
     def cache_spec(self):
         return self.mixer.cache_spec()
@@ -42,11 +44,16 @@ class PreNormBlock(Block):
         return self.mixer.first_product()
 
     def link(self, then) -> None:
+        if self.ffn is None:
+            self.mixer.then = then
+            return
         self.mixer.then = self.ffn.first_product()
         self.ffn.then = then
 
     def forward(self, stream, ctx, cache):
         h = stream.normed(self.norm1)
         stream.add(self.mixer.forward(h, ctx, cache))
+        if self.ffn is None:
+            return
         h = stream.normed(self.norm2)
         stream.add(self.ffn.forward(h, ctx))

@@ -1,0 +1,118 @@
+"""Mixers that carry a matrix of fixed size for each request and head instead of keys and values: gated linear
+attention and the generalized delta rule.  The state lives in 32-bit in a ``StateSpec`` slot of the cache manager
+(zero when a request is admitted), and one kernel walks a step's tokens of every (request, head) in order, a single
+decoded token and a portion of a prompt alike."""
+from __future__ import annotations
+
+import torch
+
+from .base import ParamSpec, StateSpec, register_part
+from .projected import ProjectedMixer
+
+
+class _Recurrent(ProjectedMixer):
+    def release_unpacked(self) -> None:
+        self._in = self.w_o = None
+
+    def in_matrices(self):
+        return list(self._in)
+
+    def out_matrix(self):
+        return self.w_o
+
+    def extra_weight_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in self._small)
+
+
+@register_part("mixer", "gla")
+class GatedLinearAttention(_Recurrent):
+    """See ``GatedLinearAttentionSpec``.  Projections q, k, v, gate and the first low-rank matrix are one product;
+    the scan kernel forms the decay (second low-rank matrix, bias, log-sigmoid / tau, exp: 32-bit) and walks the
+    tokens; a second kernel norms each head's output and gates it."""
+
+    def cache_spec(self):
+        s = self.spec
+        return StateSpec((s.heads, s.dim, s.v_dim), torch.float32)
+
+    def param_specs(self):
+        s, p = self.spec, self.prefix
+        q, k, v, g, o, norm, a1, a2, a2b = s.names
+        hd, hv = s.heads * s.dim, s.heads * s.v_dim
+        return {
+            p + q: ParamSpec((hd, s.hidden)), p + k: ParamSpec((hd, s.hidden)), p + v: ParamSpec((hv, s.hidden)),
+            p + g: ParamSpec((hv, s.hidden)), p + o: ParamSpec((s.hidden, hv)),
+            p + norm: ParamSpec((s.v_dim,), role="vector", init="one_plus_normal"),
+            p + a1: ParamSpec((-16, s.hidden)), p + a2: ParamSpec((hd, -16)), p + a2b: ParamSpec((hd,), role="vector"),
+        }
+
+    def load(self, get) -> None:
+        s, p, rt = self.spec, self.prefix, self.rt
+        q, k, v, g, o, norm, a1, a2, a2b = s.names
+        self._in = [rt.param(get(p + n)) for n in (q, k, v, g, a1)]
+        self.w_o = rt.param(get(p + o))
+        self.norm = rt.param(get(p + norm), "vector")
+        self.a2 = rt.param(get(p + a2), "vector")             # [heads * dim, rank], read in 32-bit by the scan
+        self.a2_bias = rt.param(get(p + a2b), "vector")
+        self.rank = self._in[4].shape[0]
+        if self.a2.shape[1] != self.rank:
+            raise ValueError(f"{p}: the two low-rank matrices of the decay have ranks {self.rank} and {self.a2.shape[1]}")
+        self._small = (self.norm, self.a2, self.a2_bias)
+        self.pack()
+
+    def inner_size(self) -> int:
+        return self.spec.heads * self.spec.v_dim
+
+    def core(self, y, cols, ctx, cache, out, out_col, out_scale) -> None:
+        s, ops = self.spec, self.rt.ops
+        o = torch.empty((y.shape[0], s.heads * s.v_dim), dtype=torch.float32, device=y.device)
+        ops.gla_scan(y, cols[0], cols[1], cols[2], cols[4], self.a2, self.a2_bias, 1.0 / s.tau, s.dim ** -0.5,
+                     cache.state, ctx, o, s.heads, s.dim, s.v_dim, status=ctx.status)
+        ops.head_norm_gate(o, y, cols[3], self.norm, False, s.norm_eps, "silu", out, out_col, out_scale, s.heads, s.v_dim)
+
+
+@register_part("mixer", "delta_rule")
+class DeltaRule(_Recurrent):
+    """See ``DeltaRuleSpec``.  Projections r, k, v, gate, removal rate and the first low-rank matrix of the decay are
+    one product; the scan kernel forms decay, removal rate and unit key in 32-bit and walks the tokens; a second
+    kernel norms each head's output and gates it."""
+
+    def cache_spec(self):
+        s = self.spec
+        return StateSpec((s.heads, s.dim, s.dim), torch.float32)
+
+    def param_specs(self):
+        s, p = self.spec, self.prefix
+        r, k, v, g, o, norm, a, ab, w1, w2, w0 = s.names
+        hd = s.heads * s.dim
+        out = {p + n: ParamSpec((hd, s.hidden)) for n in (r, k, v, g, a)}
+        out.update({
+            p + o: ParamSpec((s.hidden, hd)), p + norm: ParamSpec((hd,), role="vector", init="one_plus_normal"),
+            p + ab: ParamSpec((hd,), role="vector"), p + w1: ParamSpec((-16, s.hidden)), p + w2: ParamSpec((hd, -16)),
+            p + w0: ParamSpec((hd,), role="vector"),
+        })
+        return out
+
+    def load(self, get) -> None:
+        s, p, rt = self.spec, self.prefix, self.rt
+        r, k, v, g, o, norm, a, ab, w1, w2, w0 = s.names
+        self._in = [rt.param(get(p + n)) for n in (r, k, v, g, a, w1)]
+        self.w_o = rt.param(get(p + o))
+        self.norm = rt.param(get(p + norm), "vector")
+        self.a_bias = rt.param(get(p + ab), "vector")
+        self.w2 = rt.param(get(p + w2), "vector")
+        self.w0 = rt.param(get(p + w0), "vector")
+        self.rank = self._in[5].shape[0]
+        if self.w2.shape[1] != self.rank:
+            raise ValueError(f"{p}: the two low-rank matrices of the decay have ranks {self.rank} and {self.w2.shape[1]}")
+        self._small = (self.norm, self.a_bias, self.w2, self.w0)
+        self.pack()
+
+    def inner_size(self) -> int:
+        return self.spec.heads * self.spec.dim
+
+    def core(self, y, cols, ctx, cache, out, out_col, out_scale) -> None:
+        s, ops = self.spec, self.rt.ops
+        o = torch.empty((y.shape[0], s.heads * s.dim), dtype=torch.float32, device=y.device)
+        ops.delta_scan(y, cols[0], cols[1], cols[2], cols[4], cols[5], self.w2, self.w0, self.a_bias, s.decay_rate,
+                       s.key_eps, cache.state, ctx, o, s.heads, s.dim, status=ctx.status)
+        ops.head_norm_gate(o, y, cols[3], self.norm, True, s.norm_eps, "sigmoid", out, out_col, out_scale, s.heads, s.dim)

@@ -1,4 +1,4 @@
-"""Dense gated feed-forward."""
+"""Dense feed-forwards: gated, and with the PolyNorm activation."""
 from __future__ import annotations
 
 import torch
@@ -53,3 +53,38 @@ class GatedMLP(FeedForward):
         act = torch.empty((T, s.inter), dtype=h.dtype, device=h.device)
         ops.linear_silu_mul(h, self.w_gate_up, act, then=ops.product_hint(self.w_down, "stream"))
         return ops.linear_to_stream(act, self.w_down, None, then=self.then)
+
+
+@register_part("feed_forward", "polynorm_mlp")
+class PolyNormMLP(FeedForward):
+    """down(act(up(h))) without biases, act(z) = a N(z) + b N(z^2) + c N(z^3) + e with N a token's inner vector
+    divided by its root mean square: one kernel reads a row of up's result, forms the three mean squares in 32-bit
+    and writes the activation."""
+
+    graph_safe = True
+
+    def param_specs(self):
+        s, p = self.spec, self.prefix
+        u, d, act = s.names
+        return {f"{p}{u}": ParamSpec((s.inter, s.hidden)), f"{p}{d}": ParamSpec((s.hidden, s.inter)),
+                f"{p}{act}": ParamSpec((4,), role="vector", init="polynorm_coefficients")}
+
+    def load(self, get) -> None:
+        s, p, rt = self.spec, self.prefix, self.rt
+        u, d, act = s.names
+        self.w_up = rt.param(get(f"{p}{u}"))
+        self.w_down = rt.param(get(f"{p}{d}"))
+        self.coefficients = rt.param(get(f"{p}{act}"), "vector")
+
+    def weight_bytes(self) -> int:
+        return sum(m.numel() * m.element_size() for m in (self.w_up, self.w_down, self.coefficients))
+
+    def first_product(self):
+        return self.rt.ops.product_hint(self.w_up, "linear")
+
+    def forward(self, h, ctx):
+        s, ops = self.spec, self.rt.ops
+        z = torch.empty((h.shape[0], s.inter), dtype=h.dtype, device=h.device)
+        ops.linear(h, self.w_up, None, z, then=ops.product_hint(self.w_down, "stream"))
+        ops.polynorm(z, self.coefficients, s.eps, z)
+        return ops.linear_to_stream(z, self.w_down, None, then=self.then)

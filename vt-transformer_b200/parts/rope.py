@@ -44,3 +44,20 @@ class NoPosition(PositionEncoding):
 
     def load(self, get) -> None:
         self.table = None
+
+
+def rotation_frequencies(dim: int, base: float) -> torch.Tensor:
+    """[dim / 2] float32: base^(-2i/dim), formed in double and rounded once."""
+    return torch.tensor([math.pow(float(base), -2.0 * i / dim) for i in range(dim // 2)], dtype=torch.float64).to(torch.float32)
+
+
+@register_part("position", "rotary_computed")
+class ComputedRotary(PositionEncoding):
+    """The rotation of the first ``dim`` dimensions of a head, pairs (i, i + dim/2), by the angle
+    position * base^(-2i/dim): the kernel that rotates forms the angle as a 32-bit product and takes its cos and sin
+    there, so there is no table and no limit of positions.  Holds the [dim/2] frequencies on the device."""
+
+    table = None
+
+    def load(self, get) -> None:
+        self.frequencies = rotation_frequencies(self.spec.dim, self.spec.base).to(self.rt.device) if self.spec.dim else None

@@ -19,14 +19,20 @@ from typing import Optional, Tuple
 
 @dataclass(frozen=True)
 class NormSpec:
+    """``rmsnorm``: w * x / sqrt(mean(x^2) + eps).  ``layernorm``: w * (x - mean) / sqrt(var + eps), var the mean of
+    the squared deviations, no bias.  ``weight_suffix`` is appended to the part's prefix for the weight's name."""
     size: int
     eps: float
     kind: str = "rmsnorm"
+    weight_suffix: str = ".weight"
 
 
 @dataclass(frozen=True)
 class PositionSpec:
-    """``rotary``: rotation of pairs (i, i + dim/2) by pos * base^(-2i/dim).  ``none``: nothing."""
+    """``rotary``: rotation of pairs (i, i + dim/2) by pos * base^(-2i/dim), cos and sin from a table of
+    ``max_positions`` rows.  ``rotary_computed``: the same rotation of the first ``dim`` dimensions of a head (the
+    others pass), the angle formed in 32-bit from the position where it is used: no table, no limit of positions.
+    ``none``: nothing."""
     dim: int = 0
     base: float = 0.0
     max_positions: int = 0
@@ -55,7 +61,57 @@ class AttentionSpec(MixerSpec):
     scale: Optional[float] = None          # None: 1 / sqrt(head_dim)
     position: PositionSpec = field(default_factory=lambda: PositionSpec(kind="none"))
     names: Tuple[str, str, str, str] = ("q_proj", "k_proj", "v_proj", "o_proj")
+    weight_suffix: str = ".weight"         # appended to a projection's name for its matrix (".bias" for its bias)
+    v_dim: Optional[int] = None            # size of a head's value where it differs from head_dim (its keys' and queries')
+    qk_norm_eps: Optional[float] = None    # e: after the rotation q and k are divided, head by head, by sqrt(mean(.^2) + e)
+    chunk: Optional[int] = None            # c: key j is seen from position p only if j // c == p // c (counted from position 0)
     kind: str = "attention"
+
+
+@dataclass(frozen=True)
+class GatedLinearAttentionSpec(MixerSpec):
+    """Linear attention with a decay for every key channel.  For each head, with S [dim, v_dim] (32-bit, zero at the
+    start of a request): S <- diag(alpha_t) S + k_t v_t^T, o_t = S^T (q_t / sqrt(dim)), where
+    alpha = sigmoid(z)^(1 / tau) and z = A2 (A1 h) + b is a low-rank function of the input.  Each head's o is divided
+    by its root mean square (``norm_eps``) and multiplied by a weight [v_dim] shared by the heads and by
+    silu(G h); then the output projection.  ``names``: q, k, v, gate, output, the norm's weight, the two low-rank
+    matrices and the bias of the second."""
+    hidden: int = 0
+    heads: int = 0
+    dim: int = 0
+    v_dim: int = 0
+    tau: float = 1.0
+    norm_eps: float = 1e-6
+    names: Tuple[str, ...] = ("q", "k", "v", "g", "o", "norm", "a1", "a2", "a2.b")
+    kind: str = "gla"
+
+
+@dataclass(frozen=True)
+class DeltaRuleSpec(MixerSpec):
+    """The generalized delta rule.  For each head, with S [dim, dim] (32-bit, zero at the start of a request) and
+    u = k / sqrt(sum(k^2) + key_eps): S <- diag(w_t) S - (a_t * u_t)(u_t^T S) + k_t v_t^T (both terms read the old
+    S), o_t = S^T r_t, where w = exp(-decay_rate * sigmoid(W2 tanh(W1 h) + w0)) and a = sigmoid(A h + b) per head and
+    key channel.  Each head's o is divided by its root mean square (``norm_eps``); the heads together are multiplied
+    by a weight [heads * dim] and by sigmoid(G h); then the output projection.  ``names``: r, k, v, gate, output, the
+    norm's weight, the removal rate's matrix and bias, the decay's two low-rank matrices and its bias."""
+    hidden: int = 0
+    heads: int = 0
+    dim: int = 0
+    decay_rate: float = 0.6065306597126334     # exp(-1/2)
+    key_eps: float = 1e-6
+    norm_eps: float = 1e-6
+    names: Tuple[str, ...] = ("r", "k", "v", "g", "o", "norm", "a", "a.b", "w1", "w2", "w0")
+    kind: str = "delta_rule"
+
+
+@dataclass(frozen=True)
+class ParallelSpec(MixerSpec):
+    """Several mixers side by side on the same input: sum_i scales[i] * branches[i](h).  ``prefixes[i]`` is appended
+    to the part's prefix for branch i's tensors."""
+    branches: Tuple[MixerSpec, ...] = ()
+    scales: Tuple[float, ...] = ()
+    prefixes: Tuple[str, ...] = ()
+    kind: str = "parallel"
 
 
 @dataclass(frozen=True)
@@ -74,15 +130,28 @@ class GatedMLPSpec(FeedForwardSpec):
 
 
 @dataclass(frozen=True)
+class PolyNormMLPSpec(FeedForwardSpec):
+    """down(act(up(x))), no biases, with act(z) = a N(z) + b N(z^2) + c N(z^3) + e: powers element by element, N a
+    token's vector of ``inter`` values divided by its root mean square (``eps`` inside the root), and (a, b, c, e) a
+    tensor of four numbers.  ``names``: up, down, the four numbers."""
+    hidden: int = 0
+    inter: int = 0
+    eps: float = 1e-6
+    names: Tuple[str, str, str] = ("up", "down", "act")
+    kind: str = "polynorm_mlp"
+
+
+@dataclass(frozen=True)
 class BlockSpec:
-    """One layer.  ``prenorm``: x += mixer(norm1(x)); x += ffn(norm2(x)).
+    """One layer.  ``prenorm``: x += mixer(norm1(x)); x += ffn(norm2(x)).  With ``ffn`` None the layer has the
+    first sublayer only (and no second norm).
 
     ``prefix`` is the tensor-name prefix of the layer; ``mixer_prefix`` and the others
     are appended to it for the parts below it."""
     mixer: MixerSpec
-    ffn: FeedForwardSpec
+    ffn: Optional[FeedForwardSpec]
     norm1: NormSpec
-    norm2: NormSpec
+    norm2: Optional[NormSpec]
     prefix: str
     mixer_prefix: str = "self_attn."
     ffn_prefix: str = "mlp."
@@ -98,9 +167,10 @@ class RunSpec:
     Cache slots are numbered by the model; a slot belongs to the run that writes it.  A
     run with ``writes=False`` reads a slot that an earlier run wrote (shared keys and
     values) and stores nothing.  A block may appear in several runs, each with a slot of
-    its own."""
+    its own.  For a block whose mixer keeps several things (``Mixer.cache_spec`` returns a tuple) ``cache`` is a tuple
+    of slots, one for each, in that order."""
     block: int
-    cache: Optional[int]
+    cache: object               # None, a slot, or a tuple of slots
     writes: bool = True
 
 

@@ -150,7 +150,7 @@ def check_against(source: WeightSource, expected: Mapping[str, ParamSpec], ignor
         if name not in found:
             continue
         dtype, shape = found[name]
-        if tuple(shape) != tuple(spec.shape):
+        if not spec.fits(shape):
             wrong_shape[name] = (tuple(spec.shape), tuple(shape))
         if spec.role == "table":
             if dtype not in _INTS:
@@ -177,6 +177,9 @@ _INITIALISERS = {
     "one_plus_normal": lambda shape, g, sigma, device: torch.randn(shape, generator=g, dtype=torch.float32,
                                                                    device=device) * sigma + 1.0,
     "zeros": lambda shape, g, sigma, device: torch.zeros(shape, dtype=torch.float32, device=device),
+    # the four numbers of a PolyNorm activation: three weights of the order of a half that differ, and a small offset
+    "polynorm_coefficients": lambda shape, g, sigma, device: torch.tensor([0.8, 0.6, 0.3, 0.1], dtype=torch.float32, device=device)
+    + torch.randn(shape, generator=g, dtype=torch.float32, device=device) * sigma,
 }
 
 
@@ -198,14 +201,14 @@ def random_tensor(name: str, spec: ParamSpec, seed: int, sigma: float, device="c
     bfloat16; tables are zeros.  The numbers depend on (seed, name) only, not on the order in which tensors
     are made."""
     if spec.role == "table":
-        return torch.zeros(spec.shape, dtype=torch.int32, device=device)
+        return torch.zeros(spec.made_shape(), dtype=torch.int32, device=device)
     try:
         fill = _INITIALISERS[spec.init]
     except KeyError:
         raise ValueError(f"unknown initialiser '{spec.init}' for {name}; known: {', '.join(sorted(_INITIALISERS))}") from None
     g = torch.Generator(device=device)
     g.manual_seed(_tensor_seed(seed, name))
-    return fill(tuple(spec.shape), g, sigma, device).to(torch.bfloat16)
+    return fill(spec.made_shape(), g, sigma, device).to(torch.bfloat16)
 
 
 class RandomSource(WeightSource):
@@ -218,7 +221,7 @@ class RandomSource(WeightSource):
         self.where = f"random weights (seed {seed}, sigma {sigma})"
 
     def entries(self):
-        return {n: (torch.int32 if s.role == "table" else torch.bfloat16, tuple(s.shape))
+        return {n: (torch.int32 if s.role == "table" else torch.bfloat16, s.made_shape())
                 for n, s in self.expected.items()}
 
     def get(self, name: str) -> torch.Tensor:

@@ -34,7 +34,7 @@ def write_random_model(config: ModelConfig, folder: str, seed: int = 0, sigma: f
     os.makedirs(folder, exist_ok=True)
     config.save(folder)
     table = {n: s for n, s in parameter_table(config).items() if not s.optional}
-    layout = [(n, torch.int32 if s.role == "table" else torch.bfloat16, tuple(s.shape)) for n, s in table.items()]
+    layout = [(n, torch.int32 if s.role == "table" else torch.bfloat16, s.made_shape()) for n, s in table.items()]
 
     def tensors():
         for name, spec in table.items():
