@@ -161,7 +161,7 @@ def polynorm(z, coefficients, eps, out):
     out.copy_((a * n(zf) + b * n(zf * zf) + c * n(zf * zf * zf) + e).to(out.dtype))
 
 
-def head_norm_gate(o, y, gate_col, weight, weight_per_channel, eps, act, out, out_col, out_scale, heads, v_dim):
+def head_norm_gate(o, y, gate_col, weight, weight_per_channel, eps, act, out, out_col, out_scale, heads, v_dim, token_seq=None):
     T = o.shape[0]
     oh = o.view(T, heads, v_dim)
     n = oh * torch.rsqrt((oh * oh).mean(dim=-1, keepdim=True) + eps)
@@ -169,6 +169,8 @@ def head_norm_gate(o, y, gate_col, weight, weight_per_channel, eps, act, out, ou
     g = y[:, gate_col:gate_col + heads * v_dim].float().view(T, heads, v_dim)
     g = g * torch.sigmoid(g) if act == 0 else torch.sigmoid(g)
     out[:, out_col:out_col + heads * v_dim] = (out_scale * n * w * g).reshape(T, heads * v_dim).to(out.dtype)
+    if token_seq is not None:
+        out[token_seq < 0, out_col:out_col + heads * v_dim] = 0
 
 
 def _sequences(cu_q, rows):

@@ -65,8 +65,8 @@ void logits_scale_cap(Tensor& logits, double scale, double cap) {
                                               stream_of(logits)), "logits_scale_cap");
 }
 
-void rmsnorm(Tensor& x, c10::optional<Tensor> delta, const Tensor& weight, double eps, Tensor& out,
-             c10::optional<Tensor> rows, c10::optional<Tensor> status) {
+void norm_rows(bool center, Tensor& x, c10::optional<Tensor> delta, const Tensor& weight, double eps, Tensor& out,
+               c10::optional<Tensor> rows, c10::optional<Tensor> status) {
     check_f32(x, "x"); check_f32(weight, "weight"); check_cuda(out, "out");
     TORCH_CHECK(x.dim() == 2 && out.dim() == 2, "rmsnorm: x and out must be 2-d");
     const int hidden = x.size(1);
@@ -98,10 +98,153 @@ void rmsnorm(Tensor& x, c10::optional<Tensor> delta, const Tensor& weight, doubl
     }
     TORCH_CHECK(out.size(0) == n_rows, "rmsnorm: out must have one row for each normed row");
     c10::cuda::CUDAGuard guard(x.device());
-    check_launch(vtb::launch_rmsnorm(code, x.data_ptr<float>(), dp, pp, n_parts, weight.data_ptr<float>(), (float)eps,
-                                     out.data_ptr(), rp, n_rows, x.size(0), hidden, status_ptr(status),
-                                     stream_of(x)), "rmsnorm");
+    check_launch((center ? vtb::launch_layernorm : vtb::launch_rmsnorm)(code, x.data_ptr<float>(), dp, pp, n_parts,
+                                                                        weight.data_ptr<float>(), (float)eps, out.data_ptr(), rp,
+                                                                        n_rows, x.size(0), hidden, status_ptr(status),
+                                                                        stream_of(x)), center ? "layernorm" : "rmsnorm");
 }
+
+void rmsnorm(Tensor& x, c10::optional<Tensor> delta, const Tensor& weight, double eps, Tensor& out,
+             c10::optional<Tensor> rows, c10::optional<Tensor> status) {
+    norm_rows(false, x, delta, weight, eps, out, rows, status);
+}
+
+void layernorm(Tensor& x, c10::optional<Tensor> delta, const Tensor& weight, double eps, Tensor& out,
+               c10::optional<Tensor> rows, c10::optional<Tensor> status) {
+    norm_rows(true, x, delta, weight, eps, out, rows, status);
+}
+
+void polynorm(const Tensor& z, const Tensor& coef, double eps, Tensor& out) {
+    check_cuda(z, "z"); check_cuda(out, "out"); check_f32(coef, "coefficients");
+    TORCH_CHECK(z.dim() == 2 && out.sizes() == z.sizes() && out.scalar_type() == z.scalar_type(), "polynorm: out must be like z [tokens, inter]");
+    TORCH_CHECK(coef.numel() == 4, "polynorm: four coefficients");
+    TORCH_CHECK(z.size(1) % 8 == 0, "polynorm: inner size ", z.size(1), " must be a multiple of 8");
+    c10::cuda::CUDAGuard guard(z.device());
+    check_launch(vtb::launch_polynorm(dtype_code(z, "z"), z.data_ptr(), coef.data_ptr<float>(), (float)eps, out.data_ptr(), z.size(0),
+                                      z.size(1), stream_of(z)), "polynorm");
+}
+
+// columns [col, col + n) of a row-major [tokens, stride] tensor
+void check_cols(const Tensor& y, int64_t col, int64_t n, const char* what) {
+    TORCH_CHECK(col >= 0 && n >= 0 && col + n <= y.size(1), what, ": columns [", col, ", ", col + n, ") lie outside the ", y.size(1), " of y");
+}
+
+void head_norm_gate(const Tensor& o, const Tensor& y, int64_t gate_col, const Tensor& weight, bool weight_per_channel, double eps,
+                    int64_t act, Tensor& out, int64_t out_col, double out_scale, int64_t heads, int64_t v_dim,
+                    c10::optional<Tensor> token_seq) {
+    check_f32(o, "o"); check_cuda(y, "y"); check_cuda(out, "out"); check_f32(weight, "weight");
+    TORCH_CHECK(o.dim() == 2 && y.dim() == 2 && out.dim() == 2 && o.size(1) == heads * v_dim && y.size(0) == o.size(0) && out.size(0) == o.size(0),
+                "head_norm_gate: o [tokens, heads * v_dim], y and out with as many rows");
+    TORCH_CHECK(y.scalar_type() == out.scalar_type(), "head_norm_gate: y and out must have one dtype");
+    TORCH_CHECK(weight.numel() == (weight_per_channel ? heads * v_dim : v_dim), "head_norm_gate: the weight's size");
+    TORCH_CHECK(act == 0 || act == 1, "head_norm_gate: act 0 (silu) or 1 (sigmoid)");
+    check_cols(y, gate_col, heads * v_dim, "head_norm_gate (gate)"); check_cols(out, out_col, heads * v_dim, "head_norm_gate (out)");
+    const int* ts = nullptr;
+    if (token_seq.has_value()) { check_i32(*token_seq, "token_seq"); TORCH_CHECK(token_seq->numel() == o.size(0), "head_norm_gate: one sequence index a token"); ts = token_seq->data_ptr<int>(); }
+    c10::cuda::CUDAGuard guard(o.device());
+    check_launch(vtb::launch_head_norm_gate(dtype_code(y, "y"), o.data_ptr<float>(), y.data_ptr(), y.size(1), gate_col, weight.data_ptr<float>(),
+                                            weight_per_channel, (float)eps, act, out.data_ptr(), out.size(1), out_col, (float)out_scale, ts,
+                                            o.size(0), heads, v_dim, stream_of(o)), "head_norm_gate");
+}
+
+void check_scan(const Tensor& y, const Tensor& state, const Tensor& cu_q, const Tensor& rows, const Tensor& o, int64_t heads, int64_t dim,
+                int64_t v_dim, const char* who) {
+    check_cuda(y, "y"); check_f32(state, "state"); check_i32(cu_q, "cu_q"); check_i32(rows, "rows"); check_f32(o, "o");
+    TORCH_CHECK(y.dim() == 2 && o.dim() == 2 && o.size(0) == y.size(0) && o.size(1) == heads * v_dim, who, ": o must be [tokens, heads * v_dim]");
+    TORCH_CHECK(state.dim() == 4 && state.size(1) == heads && state.size(2) == dim && state.size(3) == v_dim, who,
+                ": state must be [rows, heads, dim, v_dim]");
+    TORCH_CHECK(cu_q.numel() == rows.numel() + 1, who, ": cu_q has one entry more than rows");
+}
+
+void gla_scan(const Tensor& y, int64_t q_col, int64_t k_col, int64_t v_col, int64_t low_col, const Tensor& a2, const Tensor& a2_bias,
+              double inv_tau, double q_scale, Tensor& state, const Tensor& cu_q, const Tensor& rows, Tensor& o, int64_t heads,
+              int64_t dim, int64_t v_dim, c10::optional<Tensor> status) {
+    check_scan(y, state, cu_q, rows, o, heads, dim, v_dim, "gla_scan");
+    check_f32(a2, "a2"); check_f32(a2_bias, "a2_bias");
+    TORCH_CHECK(a2.dim() == 2 && a2.size(0) == heads * dim && a2_bias.numel() == heads * dim, "gla_scan: a2 [heads * dim, rank] and its bias");
+    const int rank = a2.size(1);
+    check_cols(y, q_col, heads * dim, "gla_scan (q)"); check_cols(y, k_col, heads * dim, "gla_scan (k)");
+    check_cols(y, v_col, heads * v_dim, "gla_scan (v)"); check_cols(y, low_col, rank, "gla_scan (gate)");
+    c10::cuda::CUDAGuard guard(y.device());
+    check_launch(vtb::launch_gla_scan(dtype_code(y, "y"), y.data_ptr(), y.size(1), q_col, k_col, v_col, low_col, rank, a2.data_ptr<float>(),
+                                      a2_bias.data_ptr<float>(), (float)inv_tau, (float)q_scale, state.data_ptr<float>(), state.size(0),
+                                      cu_q.data_ptr<int>(), rows.data_ptr<int>(), rows.numel(), o.data_ptr<float>(), heads, dim, v_dim,
+                                      status_ptr(status), stream_of(y)), "gla_scan");
+}
+
+void delta_scan(const Tensor& y, int64_t r_col, int64_t k_col, int64_t v_col, int64_t a_col, int64_t low_col, const Tensor& w2,
+                const Tensor& w0, const Tensor& a_bias, double decay_rate, double key_eps, Tensor& state, const Tensor& cu_q,
+                const Tensor& rows, Tensor& o, int64_t heads, int64_t dim, c10::optional<Tensor> status) {
+    check_scan(y, state, cu_q, rows, o, heads, dim, dim, "delta_scan");
+    check_f32(w2, "w2"); check_f32(w0, "w0"); check_f32(a_bias, "a_bias");
+    TORCH_CHECK(w2.dim() == 2 && w2.size(0) == heads * dim && w0.numel() == heads * dim && a_bias.numel() == heads * dim,
+                "delta_scan: w2 [heads * dim, rank], w0 and a_bias [heads * dim]");
+    const int rank = w2.size(1);
+    for (int64_t col : {r_col, k_col, v_col, a_col}) check_cols(y, col, heads * dim, "delta_scan");
+    check_cols(y, low_col, rank, "delta_scan (decay)");
+    c10::cuda::CUDAGuard guard(y.device());
+    check_launch(vtb::launch_delta_scan(dtype_code(y, "y"), y.data_ptr(), y.size(1), r_col, k_col, v_col, a_col, low_col, rank,
+                                        w2.data_ptr<float>(), w0.data_ptr<float>(), a_bias.data_ptr<float>(), (float)decay_rate,
+                                        (float)key_eps, state.data_ptr<float>(), state.size(0), cu_q.data_ptr<int>(), rows.data_ptr<int>(),
+                                        rows.numel(), o.data_ptr<float>(), heads, dim, status_ptr(status), stream_of(y)), "delta_scan");
+}
+
+void check_pages(const Tensor& k_cache, const Tensor& v_cache, const Tensor& ref, int kv_heads, int dim, int v_dim) {
+    check_cuda(k_cache, "k_cache"); check_cuda(v_cache, "v_cache");
+    TORCH_CHECK(k_cache.dim() == 4 && v_cache.dim() == 4 && k_cache.size(0) == v_cache.size(0) && k_cache.size(2) == v_cache.size(2),
+                "cache: k [pages, kv_heads, page_size, dim] and v [pages, kv_heads, page_size, v_dim]");
+    TORCH_CHECK(k_cache.size(1) == kv_heads && v_cache.size(1) == kv_heads && k_cache.size(3) == dim && v_cache.size(3) == v_dim,
+                "cache: kv_heads, dim or v_dim differ");
+    TORCH_CHECK(k_cache.scalar_type() == ref.scalar_type() && v_cache.scalar_type() == ref.scalar_type(),
+                "cache: dtype differs from the activations'");
+}
+
+void attention_prepare(Tensor& y, int64_t q_col, int64_t k_col, int64_t v_col, const Tensor& positions, const Tensor& token_seq,
+                       c10::optional<Tensor> frequencies, double norm_eps, Tensor& k_cache, Tensor& v_cache, const Tensor& block_table,
+                       int64_t heads, int64_t kv_heads, int64_t dim, int64_t v_dim, bool store, c10::optional<Tensor> status) {
+    check_cuda(y, "y"); check_i32(positions, "positions"); check_i32(token_seq, "token_seq"); check_i32(block_table, "block_table");
+    TORCH_CHECK(y.dim() == 2 && positions.numel() == y.size(0) && token_seq.numel() == y.size(0), "attention_prepare: one position and sequence a token");
+    TORCH_CHECK(block_table.dim() == 2, "attention_prepare: block_table must be [sequences, stride]");
+    check_cols(y, q_col, heads * dim, "attention_prepare (q)"); check_cols(y, k_col, kv_heads * dim, "attention_prepare (k)");
+    check_cols(y, v_col, kv_heads * v_dim, "attention_prepare (v)");
+    check_pages(k_cache, v_cache, y, kv_heads, dim, v_dim);
+    const float* fp = nullptr;
+    int half = 0;
+    if (frequencies.has_value()) {
+        check_f32(*frequencies, "frequencies");
+        fp = frequencies->data_ptr<float>();
+        half = frequencies->numel();
+        TORCH_CHECK(2 * half <= dim, "attention_prepare: the rotation covers more than the head");
+    }
+    TORCH_CHECK(dim <= 256, "attention_prepare: head sizes up to 256");
+    c10::cuda::CUDAGuard guard(y.device());
+    check_launch(vtb::launch_attention_prepare(dtype_code(y, "y"), y.data_ptr(), y.size(1), q_col, k_col, v_col, positions.data_ptr<int>(),
+                                               token_seq.data_ptr<int>(), fp, half, (float)norm_eps, k_cache.data_ptr(), v_cache.data_ptr(),
+                                               block_table.data_ptr<int>(), block_table.size(1), block_table.size(0), k_cache.size(0),
+                                               y.size(0), heads, kv_heads, dim, v_dim, k_cache.size(2), store ? 1 : 0, status_ptr(status),
+                                               stream_of(y)), "attention_prepare");
+}
+
+void attention_general(const Tensor& y, int64_t q_col, Tensor& out, int64_t out_col, double out_scale, const Tensor& k_cache,
+                       const Tensor& v_cache, const Tensor& positions, const Tensor& token_seq, const Tensor& block_table, int64_t heads,
+                       int64_t kv_heads, int64_t dim, int64_t v_dim, int64_t window, int64_t chunk, double scale, c10::optional<Tensor> status) {
+    check_cuda(y, "y"); check_cuda(out, "out"); check_i32(positions, "positions"); check_i32(token_seq, "token_seq");
+    check_i32(block_table, "block_table");
+    TORCH_CHECK(y.dim() == 2 && out.dim() == 2 && out.size(0) == y.size(0) && out.scalar_type() == y.scalar_type(),
+                "attention_general: y and out [tokens, .] of one dtype");
+    TORCH_CHECK(positions.numel() == y.size(0) && token_seq.numel() == y.size(0), "attention_general: one position and sequence a token");
+    TORCH_CHECK(block_table.dim() == 2 && heads % kv_heads == 0, "attention_general: block_table [sequences, stride]; heads a multiple of kv_heads");
+    check_cols(y, q_col, heads * dim, "attention_general (q)"); check_cols(out, out_col, heads * v_dim, "attention_general (out)");
+    check_pages(k_cache, v_cache, y, kv_heads, dim, v_dim);
+    TORCH_CHECK(dim <= 256 && v_dim <= 256, "attention_general: head sizes up to 256");
+    c10::cuda::CUDAGuard guard(y.device());
+    check_launch(vtb::launch_attention_general(dtype_code(y, "y"), y.data_ptr(), y.size(1), q_col, out.data_ptr(), out.size(1), out_col,
+                                               (float)out_scale, k_cache.data_ptr(), v_cache.data_ptr(), positions.data_ptr<int>(),
+                                               token_seq.data_ptr<int>(), block_table.data_ptr<int>(), block_table.size(1),
+                                               block_table.size(0), k_cache.size(0), y.size(0), heads, kv_heads, dim, v_dim, k_cache.size(2),
+                                               window, chunk, (float)scale, status_ptr(status), stream_of(y)), "attention_general");
+}
+
 
 void silu_mul(const Tensor& gu, Tensor& out, int64_t interleave) {
     check_cuda(gu, "gu"); check_cuda(out, "out");
@@ -500,6 +643,16 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("logits_scale_cap", &logits_scale_cap, py::arg("logits"), py::arg("scale"), py::arg("cap"));
     m.def("rmsnorm", &rmsnorm, py::arg("x"), py::arg("delta"), py::arg("weight"), py::arg("eps"), py::arg("out"),
           py::arg("rows") = py::none(), py::arg("status") = py::none());
+    m.def("layernorm", &layernorm, py::arg("x"), py::arg("delta"), py::arg("weight"), py::arg("eps"), py::arg("out"),
+          py::arg("rows") = py::none(), py::arg("status") = py::none());
+    m.def("polynorm", &polynorm);
+    m.def("head_norm_gate", &head_norm_gate, py::arg("o"), py::arg("y"), py::arg("gate_col"), py::arg("weight"),
+          py::arg("weight_per_channel"), py::arg("eps"), py::arg("act"), py::arg("out"), py::arg("out_col"), py::arg("out_scale"),
+          py::arg("heads"), py::arg("v_dim"), py::arg("token_seq") = py::none());
+    m.def("gla_scan", &gla_scan);
+    m.def("delta_scan", &delta_scan);
+    m.def("attention_prepare", &attention_prepare);
+    m.def("attention_general", &attention_general);
     m.def("silu_mul", &silu_mul, py::arg("gu"), py::arg("out"), py::arg("interleave") = 0);
     m.def("rope_store", &rope_store, py::arg("qkv"), py::arg("positions"), py::arg("cos_sin"), py::arg("k_cache"),
           py::arg("v_cache"), py::arg("token_seq"), py::arg("block_table"), py::arg("heads"), py::arg("kv_heads"),

@@ -34,6 +34,8 @@ SOURCES = [
     "gemm_tc_pair.cu",
     "attention_noalloc.cu",
     "sampling.cu",
+    "recurrent.cu",
+    "attention_general.cu",
 ]
 HEADERS = ["common.cuh", "kernels.h", "launch.cuh", "tc_common.cuh", "gemm_epilogue.cuh", "attention_mma.cuh", "attention_decode.cuh", "attention_noalloc.h"]
 

@@ -80,7 +80,7 @@ cudaError_t launch_logits_scale_cap(float* logits, long long n, float scale, flo
 // depends on hidden and the block size only, never on the batch.  The delta may also come as `n_parts` 32-bit
 // shares [n_parts, n_tokens, hidden] (a matrix product whose inner dimension was cut over CTAs leaves its shares
 // unadded): they are added here in the order of their index.
-template <typename T>
+template <typename T, bool Center>
 __global__ void rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta, const float* __restrict__ parts,
                                int n_parts, const float* __restrict__ weight, float eps, T* __restrict__ out,
                                const int* __restrict__ rows, int n_tokens, int hidden, int* status) {
@@ -121,8 +121,8 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delt
     };
     const int first = threadIdx.x * 8;
     const bool once = hidden <= (int)blockDim.x * 8;      // a thread has all its values at once: they stay in registers
-    float keep[8];
-    float ss = 0.f;
+    float keep[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    float ss = 0.f, sm = 0.f;
     for (int i = first; i < hidden; i += blockDim.x * 8) {
         float v[8];
         row_values(i, v);
@@ -130,7 +130,25 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delt
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             ss += v[j] * v[j];
+            sm += v[j];
             keep[j] = v[j];
+        }
+    }
+    float mean = 0.f;
+    if (Center) {
+        // the layer norm: the mean first, then the mean of the squared deviations from it (not E[v^2] - mean^2)
+        mean = block_sum(sm, scratch) / (float)hidden;
+        ss = 0.f;
+        for (int i = first; i < hidden; i += blockDim.x * 8) {
+            float v[8];
+            if (once) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = keep[j];
+            } else {
+                Vec8<float>::load(xr + i, v);
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) ss += (v[j] - mean) * (v[j] - mean);
         }
     }
     const float total = block_sum(ss, scratch);
@@ -150,22 +168,86 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delt
             Vec8<float>::load(weight + i, w);
         }
 #pragma unroll
-        for (int j = 0; j < 8; ++j) y[j] = w[j] * v[j] * rs;
+        for (int j = 0; j < 8; ++j) y[j] = w[j] * (v[j] - mean) * rs;
         Vec8<T>::store(o + i, y);
     }
+}
+
+template <bool Center>
+static cudaError_t launch_norm(int out_dtype, float* x, const void* delta, const float* parts, int n_parts,
+                               const float* weight, float eps, void* out, const int* rows, int n_rows, int n_tokens,
+                               int hidden, int* status, cudaStream_t stream) {
+    if (delta != nullptr && parts != nullptr) return cudaErrorInvalidValue;
+    if (n_rows == 0) return cudaSuccess;
+    int threads = min(512, max(32, ((hidden / 8 + 31) / 32) * 32));
+    if (out_dtype == kBF16)
+        return launch(rmsnorm_kernel<__nv_bfloat16, Center>, n_rows, threads, 0, stream, x, (const __nv_bfloat16*)delta, parts, n_parts, weight, eps,
+                      (__nv_bfloat16*)out, rows, n_tokens, hidden, status);
+    return launch(rmsnorm_kernel<float, Center>, n_rows, threads, 0, stream, x, (const float*)delta, parts, n_parts, weight, eps, (float*)out, rows, n_tokens,
+                  hidden, status);
 }
 
 cudaError_t launch_rmsnorm(int out_dtype, float* x, const void* delta, const float* parts, int n_parts,
                            const float* weight, float eps, void* out, const int* rows, int n_rows, int n_tokens,
                            int hidden, int* status, cudaStream_t stream) {
-    if (delta != nullptr && parts != nullptr) return cudaErrorInvalidValue;
-    if (n_rows == 0) return cudaSuccess;
-    int threads = min(512, max(32, ((hidden / 8 + 31) / 32) * 32));
-    if (out_dtype == kBF16)
-        return launch(rmsnorm_kernel<__nv_bfloat16>, n_rows, threads, 0, stream, x, (const __nv_bfloat16*)delta, parts, n_parts, weight, eps,
-                      (__nv_bfloat16*)out, rows, n_tokens, hidden, status);
-    return launch(rmsnorm_kernel<float>, n_rows, threads, 0, stream, x, (const float*)delta, parts, n_parts, weight, eps, (float*)out, rows, n_tokens,
-                  hidden, status);
+    return launch_norm<false>(out_dtype, x, delta, parts, n_parts, weight, eps, out, rows, n_rows, n_tokens, hidden, status, stream);
+}
+
+cudaError_t launch_layernorm(int out_dtype, float* x, const void* delta, const float* parts, int n_parts,
+                             const float* weight, float eps, void* out, const int* rows, int n_rows, int n_tokens,
+                             int hidden, int* status, cudaStream_t stream) {
+    return launch_norm<true>(out_dtype, x, delta, parts, n_parts, weight, eps, out, rows, n_rows, n_tokens, hidden, status, stream);
+}
+
+// ------------------------------------------------------------------------- PolyNorm
+
+// One block a row: out = a N(z) + b N(z^2) + c N(z^3) + e with N(y) = y / sqrt(mean(y^2) + eps).  Pass 1 sums z^2,
+// z^4 and z^6 in 32-bit; pass 2 reads the row again (each thread the values it read before, so `out` may be `z`).
+template <typename T>
+__global__ void polynorm_kernel(const T* __restrict__ z, const float* __restrict__ coef, float eps, T* __restrict__ out,
+                                int inter) {
+    __shared__ float scratch[32];
+    pdl_launch();
+    const float a = coef[0], b = coef[1], c = coef[2], e = coef[3];      // weights: written by no kernel of the step
+    pdl_wait();
+    const T* zr = z + (size_t)blockIdx.x * inter;
+    T* o = out + (size_t)blockIdx.x * inter;
+    float s2 = 0.f, s4 = 0.f, s6 = 0.f;
+    for (int i = threadIdx.x * 8; i < inter; i += blockDim.x * 8) {
+        float v[8];
+        Vec8<T>::load(zr + i, v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float p2 = v[j] * v[j];
+            s2 += p2;
+            s4 = fmaf(p2, p2, s4);
+            s6 = fmaf(p2 * p2, p2, s6);
+        }
+    }
+    const float n = (float)inter;
+    const float r1 = a * rsqrtf(block_sum(s2, scratch) / n + eps);
+    const float r2 = b * rsqrtf(block_sum(s4, scratch) / n + eps);
+    const float r3 = c * rsqrtf(block_sum(s6, scratch) / n + eps);
+    for (int i = threadIdx.x * 8; i < inter; i += blockDim.x * 8) {
+        float v[8], y[8];
+        Vec8<T>::load(zr + i, v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float p2 = v[j] * v[j];
+            y[j] = fmaf(r1, v[j], fmaf(r2, p2, fmaf(r3, p2 * v[j], e)));
+        }
+        Vec8<T>::store(o + i, y);
+    }
+}
+
+cudaError_t launch_polynorm(int dtype, const void* z, const float* coef, float eps, void* out, int n_tokens, int inter,
+                            cudaStream_t stream) {
+    if (n_tokens == 0) return cudaSuccess;
+    if (inter % 8) return cudaErrorInvalidValue;
+    const int threads = min(512, max(32, ((inter / 8 + 31) / 32) * 32));
+    if (dtype == kBF16)
+        return launch(polynorm_kernel<__nv_bfloat16>, n_tokens, threads, 0, stream, (const __nv_bfloat16*)z, coef, eps, (__nv_bfloat16*)out, inter);
+    return launch(polynorm_kernel<float>, n_tokens, threads, 0, stream, (const float*)z, coef, eps, (float*)out, inter);
 }
 
 // ------------------------------------------------------------------------- silu * up

@@ -23,6 +23,53 @@ cudaError_t launch_rmsnorm(int out_dtype, float* x, const void* delta, const flo
                            const float* weight, float eps, void* out, const int* rows, int n_rows, int n_tokens,
                            int hidden, int* status, cudaStream_t stream);
 
+// The same with the mean taken off: out[r] = weight * (v - mean(v)) * rsqrt(mean((v - mean(v))^2) + eps).
+cudaError_t launch_layernorm(int out_dtype, float* x, const void* delta, const float* parts, int n_parts,
+                             const float* weight, float eps, void* out, const int* rows, int n_rows, int n_tokens,
+                             int hidden, int* status, cudaStream_t stream);
+
+// out[t, :] = a N(z) + b N(z^2) + c N(z^3) + e for every row of z [n_tokens, inter], N(y) = y / sqrt(mean(y^2) + eps),
+// (a, b, c, e) = coef[0..3].  out may be z.  inter % 8 == 0.
+cudaError_t launch_polynorm(int dtype, const void* z, const float* coef, float eps, void* out, int n_tokens, int inter,
+                            cudaStream_t stream);
+
+// Gated linear attention over the tokens of every (sequence, head) in order (recurrent.cu).  y [tokens, stride] holds
+// q, k [heads * dim], v [heads * v_dim] and the low-rank gate's input [rank] at the given columns; a2 [heads * dim,
+// rank] and a2_bias are float; state [state_rows, heads, dim, v_dim] float is read at rows[sequence] and left as after
+// the sequence's last token; out [tokens, heads * v_dim] float.  A sequence without tokens is left alone.
+cudaError_t launch_gla_scan(int dtype, const void* y, int stride, int q_col, int k_col, int v_col, int low_col, int rank,
+                            const float* a2, const float* a2_bias, float inv_tau, float q_scale, float* state,
+                            int state_rows, const int* cu_q, const int* rows, int n_seqs, float* out, int heads, int dim,
+                            int v_dim, int* status, cudaStream_t stream);
+// The generalized delta rule in the same manner; a_col: the removal rate's projection, low_col: the decay's low-rank
+// input (tanh is applied to it), w2 [heads * dim, rank], w0 and a_bias float; state [state_rows, heads, dim, dim].
+cudaError_t launch_delta_scan(int dtype, const void* y, int stride, int r_col, int k_col, int v_col, int a_col, int low_col,
+                              int rank, const float* w2, const float* w0, const float* a_bias, float decay_rate,
+                              float key_eps, float* state, int state_rows, const int* cu_q, const int* rows, int n_seqs,
+                              float* out, int heads, int dim, int* status, cudaStream_t stream);
+// out[t, out_col + h v_dim + i] = out_scale * o[t, h, i] * rsqrt(mean_i o[t, h, :]^2 + eps) * w * act(y[t, gate_col + h v_dim + i]);
+// w = weight[i], or weight[h v_dim + i] with weight_per_channel; act 0: silu, 1: sigmoid.  token_seq (may be null): rows
+// of padding tokens (< 0) become zero.
+cudaError_t launch_head_norm_gate(int dtype, const float* o, const void* y, int y_stride, int gate_col, const float* weight,
+                                  int weight_per_channel, float eps, int act, void* out, int out_stride, int out_col,
+                                  float out_scale, const int* token_seq, int n_tokens, int heads, int v_dim, cudaStream_t stream);
+
+// The general attention (attention_general.cu).  Prepare: q [heads * dim] and k [kv_heads * dim] at their columns of y
+// are rotated (pairs (i, i + half) of each head's first 2 half dimensions, angle position * freq[i]) and, with
+// norm_eps >= 0, divided head by head by sqrt(mean(.^2) + norm_eps); q is written back, k and v [kv_heads * v_dim] go
+// into k_cache [pages, kv_heads, page_size, dim] and v_cache [.., v_dim] if store.
+cudaError_t launch_attention_prepare(int dtype, void* y, int stride, int q_col, int k_col, int v_col, const int* positions,
+                                     const int* token_seq, const float* freq, int half, float norm_eps, void* k_cache,
+                                     void* v_cache, const int* block_table, int table_stride, int n_seqs, int n_pages,
+                                     int n_tokens, int heads, int kv_heads, int dim, int v_dim, int page_size, int store,
+                                     int* status, cudaStream_t stream);
+// Token t at position p sees keys j <= p with j > p - window (window > 0) and j / chunk == p / chunk (chunk > 0).
+cudaError_t launch_attention_general(int dtype, const void* y, int stride, int q_col, void* out, int out_stride, int out_col,
+                                     float out_scale, const void* k_cache, const void* v_cache, const int* positions,
+                                     const int* token_seq, const int* block_table, int table_stride, int n_seqs, int n_pages,
+                                     int n_tokens, int heads, int kv_heads, int dim, int v_dim, int page_size, int window,
+                                     int chunk, float scale, int* status, cudaStream_t stream);
+
 // out[t, i] = silu(gate) * up.  interleave 0: gate = gu[t, i], up = gu[t, inter + i].  interleave 8: gate and up
 // columns alternate in runs of 8 (g0..g7, u0..u7, g8.., ...): gate = gu[t, 16 (i / 8) + i % 8], up 8 further.
 // inter % 8 == 0.

@@ -1,0 +1,308 @@
+// Mixers that carry a matrix of fixed size for each (request, head): gated linear attention and the generalized
+// delta rule, and the norm-and-gate step that follows them.
+//
+// The recurrences, for one head with state S [dim, v_dim] in 32-bit:
+//   gated linear attention   S <- diag(alpha_t) S + k_t v_t^T,                         o_t = S^T q_t
+//   delta rule               S <- diag(w_t) S - (a_t * u_t)(u_t^T S_old) + k_t v_t^T,  o_t = S^T r_t
+// Column j of S depends on column j alone, so a CTA owns 32 columns of one (sequence, head) and walks the step's
+// tokens of that sequence in order: a decoded token and a portion of a prompt are the same loop.  A thread keeps
+// KD rows of its column in registers; with dim > KD the rows are spread over `G` threads a column, whose partial dot
+// products meet in shared memory in the order of g.  What enters the recurrence is formed in 32-bit while a batch of
+// tokens is staged in shared memory: the decay from its low-rank gate (log-sigmoid and exp, or sigmoid and exp), the
+// removal rate, the unit key.  The sums' order depends on dim alone, never on how the tokens were cut into steps.
+#include "common.cuh"
+#include "kernels.h"
+#include "launch.cuh"
+
+namespace vtb {
+
+namespace {
+
+constexpr int kScanCols = 32;     // columns of the state a CTA owns (one warp for each group of rows)
+constexpr int kScanTokens = 8;    // tokens staged in shared memory at once
+
+struct ScanArgs {
+    const void* y;                // [tokens, stride]: the projections
+    int stride;
+    int q_col, k_col, v_col;      // q (or r), k, v
+    int a_col;                    // delta rule: the removal rate's projection
+    int low_col, rank;            // the low-rank gate's input
+    const float* w2;              // [heads * dim, rank]
+    const float* bias2;           // [heads * dim]: bias of the low-rank gate
+    const float* a_bias;          // [heads * dim] (delta rule)
+    float c1;                     // gated linear attention: 1 / tau;  delta rule: the decay's rate
+    float c2;                     // gated linear attention: the scale of q;  delta rule: eps of the unit key
+    float* state;                 // [state rows, heads, dim, v_dim]
+    int state_rows;
+    const int* cu_q;              // [sequences + 1]
+    const int* rows;              // [sequences]
+    float* out;                   // [tokens, heads * v_dim]
+    int heads, dim, v_dim, groups;
+    int* status;
+};
+
+__device__ __forceinline__ float log_sigmoid(float z) {
+    // log(1 / (1 + exp(-z))) without overflow on either side
+    return z < 0.f ? z - log1pf(expf(z)) : -log1pf(expf(-z));
+}
+
+__device__ __forceinline__ float sigmoid(float z) { return 1.f / (1.f + expf(-z)); }
+
+template <typename T, int KD, bool Delta>
+__global__ void __launch_bounds__(kScanCols * 8)
+scan_kernel(const ScanArgs a) {
+    extern __shared__ __align__(16) float smem[];
+    pdl_launch();
+    const int seq = blockIdx.x, h = blockIdx.y;
+    const int c = threadIdx.x, g = threadIdx.y;
+    const int G = a.groups;
+    const int tid = g * kScanCols + c, n_threads = kScanCols * G;
+    const int dim = a.dim, v_dim = a.v_dim, rank = a.rank;
+    const int dim_p = G * KD;
+    const int j = blockIdx.z * kScanCols + c;
+    const bool col_ok = j < v_dim;
+    // shared memory: the low-rank gate's second matrix for this head; a batch of tokens; the meeting place of the groups
+    float* w2s = smem;                                   // [dim, rank]
+    float* low = w2s + ((dim * rank + 3) & ~3);          // [tokens, rank]
+    float* qs = low + ((kScanTokens * rank + 3) & ~3);   // [tokens, dim_p] each:
+    float* ks = qs + kScanTokens * dim_p;
+    float* ds = ks + kScanTokens * dim_p;
+    float* us = ds + kScanTokens * dim_p;                // delta rule: the unit key
+    float* bs = us + (Delta ? kScanTokens * dim_p : 0);  // delta rule: removal rate times unit key
+    float* vs = bs + (Delta ? kScanTokens * dim_p : 0);  // [tokens, 32]
+    float* red = vs + kScanTokens * kScanCols;           // [2, G, 32]
+    // the weights are written by no kernel of the step: they are read before the wait
+    for (int e = tid; e < dim * rank; e += n_threads) w2s[e] = a.w2[(size_t)h * dim * rank + e];
+    pdl_wait();
+    const int t0 = a.cu_q[seq], t1 = a.cu_q[seq + 1];
+    if (t1 <= t0) return;                                // a sequence without tokens in this step (padding): its state stays
+    const int row = a.rows[seq];
+    if (row < 0 || row >= a.state_rows) {
+        if (tid == 0) set_status(a.status, kStatusBadRow, row);
+        return;
+    }
+    const T* y = reinterpret_cast<const T*>(a.y);
+    float* sp = a.state + (((size_t)row * a.heads + h) * dim) * v_dim;
+    float S[KD];
+#pragma unroll
+    for (int i = 0; i < KD; ++i) {
+        const int r = g * KD + i;
+        S[i] = (col_ok && r < dim) ? sp[(size_t)r * v_dim + j] : 0.f;
+    }
+    int meet = 0;
+    for (int tb0 = t0; tb0 < t1; tb0 += kScanTokens) {
+        const int n = min(kScanTokens, t1 - tb0);
+        __syncthreads();                                 // the batch before is done with
+        for (int e = tid; e < n * rank; e += n_threads) {
+            const float v = to_float(y[(size_t)(tb0 + e / rank) * a.stride + a.low_col + e % rank]);
+            low[e] = Delta ? tanhf(v) : v;
+        }
+        for (int e = tid; e < n * kScanCols; e += n_threads) {
+            const int jj = blockIdx.z * kScanCols + e % kScanCols;
+            vs[e] = jj < v_dim ? to_float(y[(size_t)(tb0 + e / kScanCols) * a.stride + a.v_col + h * v_dim + jj]) : 0.f;
+        }
+        __syncthreads();
+        for (int e = tid; e < n * dim_p; e += n_threads) {
+            const int tb = e / dim_p, i = e % dim_p;
+            float q = 0.f, k = 0.f, d = 0.f, b = 0.f;
+            if (i < dim) {
+                const T* yr = y + (size_t)(tb0 + tb) * a.stride;
+                const int ch = h * dim + i;
+                q = to_float(yr[a.q_col + ch]);
+                k = to_float(yr[a.k_col + ch]);
+                float z = a.bias2[ch];
+                const float* wr = w2s + i * rank;
+                const float* lr = low + tb * rank;
+                for (int r = 0; r < rank; ++r) z = fmaf(wr[r], lr[r], z);
+                if (Delta) {
+                    d = expf(-a.c1 * sigmoid(z));
+                    b = sigmoid(to_float(yr[a.a_col + ch]) + a.a_bias[ch]);
+                } else {
+                    d = expf(a.c1 * log_sigmoid(z));
+                    q *= a.c2;
+                }
+            }
+            qs[e] = q; ks[e] = k; ds[e] = d;
+            if (Delta) bs[e] = b;
+        }
+        __syncthreads();
+        if (Delta) {
+            // the unit key u = k / sqrt(sum(k^2) + eps), and b = a * u: a warp for each staged token
+            for (int tb = g; tb < n; tb += G) {
+                float ss = 0.f;
+                for (int i = c; i < dim_p; i += 32) ss = fmaf(ks[tb * dim_p + i], ks[tb * dim_p + i], ss);
+                ss = warp_sum(ss);
+                const float inv = 1.f / sqrtf(ss + a.c2);
+                for (int i = c; i < dim_p; i += 32) {
+                    const float u = ks[tb * dim_p + i] * inv;
+                    us[tb * dim_p + i] = u;
+                    bs[tb * dim_p + i] *= u;
+                }
+            }
+            __syncthreads();
+        }
+        for (int tb = 0; tb < n; ++tb) {
+            const float v = vs[tb * kScanCols + c];
+            const float4* q4 = reinterpret_cast<const float4*>(qs + tb * dim_p + g * KD);
+            const float4* k4 = reinterpret_cast<const float4*>(ks + tb * dim_p + g * KD);
+            const float4* d4 = reinterpret_cast<const float4*>(ds + tb * dim_p + g * KD);
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            if (Delta) {
+                const float4* u4 = reinterpret_cast<const float4*>(us + tb * dim_p + g * KD);
+                const float4* b4 = reinterpret_cast<const float4*>(bs + tb * dim_p + g * KD);
+                float part[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int i = 0; i < KD / 4; ++i) {
+                    const float4 u = u4[i];
+                    part[0] = fmaf(u.x, S[4 * i + 0], part[0]);
+                    part[1] = fmaf(u.y, S[4 * i + 1], part[1]);
+                    part[2] = fmaf(u.z, S[4 * i + 2], part[2]);
+                    part[3] = fmaf(u.w, S[4 * i + 3], part[3]);
+                }
+                float us_old = (part[0] + part[1]) + (part[2] + part[3]);
+                if (G > 1) {
+                    float* m = red + (meet++ & 1) * G * kScanCols;
+                    m[g * kScanCols + c] = us_old;
+                    __syncthreads();
+                    us_old = 0.f;
+                    for (int gg = 0; gg < G; ++gg) us_old += m[gg * kScanCols + c];
+                }
+#pragma unroll
+                for (int i = 0; i < KD / 4; ++i) {
+                    const float4 q = q4[i], k = k4[i], d = d4[i], b = b4[i];
+                    S[4 * i + 0] = fmaf(d.x, S[4 * i + 0], fmaf(k.x, v, -b.x * us_old));
+                    S[4 * i + 1] = fmaf(d.y, S[4 * i + 1], fmaf(k.y, v, -b.y * us_old));
+                    S[4 * i + 2] = fmaf(d.z, S[4 * i + 2], fmaf(k.z, v, -b.z * us_old));
+                    S[4 * i + 3] = fmaf(d.w, S[4 * i + 3], fmaf(k.w, v, -b.w * us_old));
+                    acc[0] = fmaf(S[4 * i + 0], q.x, acc[0]);
+                    acc[1] = fmaf(S[4 * i + 1], q.y, acc[1]);
+                    acc[2] = fmaf(S[4 * i + 2], q.z, acc[2]);
+                    acc[3] = fmaf(S[4 * i + 3], q.w, acc[3]);
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < KD / 4; ++i) {
+                    const float4 q = q4[i], k = k4[i], d = d4[i];
+                    S[4 * i + 0] = fmaf(d.x, S[4 * i + 0], k.x * v);
+                    S[4 * i + 1] = fmaf(d.y, S[4 * i + 1], k.y * v);
+                    S[4 * i + 2] = fmaf(d.z, S[4 * i + 2], k.z * v);
+                    S[4 * i + 3] = fmaf(d.w, S[4 * i + 3], k.w * v);
+                    acc[0] = fmaf(S[4 * i + 0], q.x, acc[0]);
+                    acc[1] = fmaf(S[4 * i + 1], q.y, acc[1]);
+                    acc[2] = fmaf(S[4 * i + 2], q.z, acc[2]);
+                    acc[3] = fmaf(S[4 * i + 3], q.w, acc[3]);
+                }
+            }
+            float o = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+            if (G > 1) {
+                float* m = red + (meet++ & 1) * G * kScanCols;
+                m[g * kScanCols + c] = o;
+                __syncthreads();
+                o = 0.f;
+                for (int gg = 0; gg < G; ++gg) o += m[gg * kScanCols + c];
+            }
+            if (g == 0 && col_ok) a.out[(size_t)(tb0 + tb) * a.heads * v_dim + h * v_dim + j] = o;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < KD; ++i) {
+        const int r = g * KD + i;
+        if (col_ok && r < dim) sp[(size_t)r * v_dim + j] = S[i];
+    }
+}
+
+template <typename T, int KD, bool Delta>
+cudaError_t launch_scan_kd(const ScanArgs& a, int n_seqs, cudaStream_t stream) {
+    static std::atomic<unsigned long long> done{0};
+    const int G = a.groups, dim_p = G * KD;
+    const size_t floats = ((a.dim * a.rank + 3) & ~3) + ((kScanTokens * a.rank + 3) & ~3)
+                          + (size_t)(Delta ? 5 : 3) * kScanTokens * dim_p + kScanTokens * kScanCols + 2 * G * kScanCols;
+    const size_t bytes = floats * sizeof(float);
+    if (bytes > 200 * 1024) return cudaErrorInvalidValue;
+    cudaError_t e = allow_dynamic_smem(scan_kernel<T, KD, Delta>, (int)bytes, done);
+    if (e != cudaSuccess) return e;
+    dim3 grid(n_seqs, a.heads, (a.v_dim + kScanCols - 1) / kScanCols), block(kScanCols, G);
+    return launch(scan_kernel<T, KD, Delta>, grid, block, bytes, stream, a);
+}
+
+template <typename T, bool Delta>
+cudaError_t launch_scan_t(ScanArgs a, int n_seqs, cudaStream_t stream) {
+    // rows a thread: the smallest of 32, 64, 128 that holds dim; beyond 128 the rows are spread over groups of 128
+    if (a.dim <= 32) { a.groups = 1; return launch_scan_kd<T, 32, Delta>(a, n_seqs, stream); }
+    if (a.dim <= 64) { a.groups = 1; return launch_scan_kd<T, 64, Delta>(a, n_seqs, stream); }
+    a.groups = (a.dim + 127) / 128;
+    if (a.groups > 8) return cudaErrorInvalidValue;
+    return launch_scan_kd<T, 128, Delta>(a, n_seqs, stream);
+}
+
+}  // namespace
+
+cudaError_t launch_gla_scan(int dtype, const void* y, int stride, int q_col, int k_col, int v_col, int low_col, int rank,
+                            const float* a2, const float* a2_bias, float inv_tau, float q_scale, float* state,
+                            int state_rows, const int* cu_q, const int* rows, int n_seqs, float* out, int heads, int dim,
+                            int v_dim, int* status, cudaStream_t stream) {
+    if (n_seqs == 0) return cudaSuccess;
+    ScanArgs a = {y, stride, q_col, k_col, v_col, 0, low_col, rank, a2, a2_bias, nullptr, inv_tau, q_scale, state,
+                  state_rows, cu_q, rows, out, heads, dim, v_dim, 1, status};
+    return dtype == kBF16 ? launch_scan_t<__nv_bfloat16, false>(a, n_seqs, stream) : launch_scan_t<float, false>(a, n_seqs, stream);
+}
+
+cudaError_t launch_delta_scan(int dtype, const void* y, int stride, int r_col, int k_col, int v_col, int a_col, int low_col,
+                              int rank, const float* w2, const float* w0, const float* a_bias, float decay_rate,
+                              float key_eps, float* state, int state_rows, const int* cu_q, const int* rows, int n_seqs,
+                              float* out, int heads, int dim, int* status, cudaStream_t stream) {
+    if (n_seqs == 0) return cudaSuccess;
+    ScanArgs a = {y, stride, r_col, k_col, v_col, a_col, low_col, rank, w2, w0, a_bias, decay_rate, key_eps, state,
+                  state_rows, cu_q, rows, out, heads, dim, dim, 1, status};
+    return dtype == kBF16 ? launch_scan_t<__nv_bfloat16, true>(a, n_seqs, stream) : launch_scan_t<float, true>(a, n_seqs, stream);
+}
+
+// ------------------------------------------------------------------------- norm of each head's output, gate
+
+// One warp for a (token, head): out = out_scale * o / sqrt(mean(o^2) + eps) * w * act(gate), all in 32-bit.
+template <typename T>
+__global__ void __launch_bounds__(128)
+head_norm_gate_kernel(const float* __restrict__ o, const T* __restrict__ y, int y_stride, int gate_col,
+                      const float* __restrict__ weight, int weight_per_channel, float eps, int act, T* __restrict__ out,
+                      int out_stride, int out_col, float out_scale, const int* __restrict__ token_seq, int n_tokens, int heads,
+                      int v_dim) {
+    pdl_launch();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const long long pair = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (pair >= (long long)n_tokens * heads) return;
+    const int t = (int)(pair / heads), h = (int)(pair % heads);
+    T* dst = out + (size_t)t * out_stride + out_col + h * v_dim;
+    if (token_seq != nullptr && token_seq[t] < 0) {     // padding: nothing ran for this token
+        for (int i = lane; i < v_dim; i += 32) dst[i] = from_float<T>(0.f);
+        return;
+    }
+    const float* src = o + ((size_t)t * heads + h) * v_dim;
+    float ss = 0.f;
+    for (int i = lane; i < v_dim; i += 32) ss = fmaf(src[i], src[i], ss);
+    ss = warp_sum(ss);
+    const float r = rsqrtf(ss / (float)v_dim + eps) * out_scale;
+    const T* gate = y + (size_t)t * y_stride + gate_col + h * v_dim;
+    const float* w = weight + (weight_per_channel ? h * v_dim : 0);
+    for (int i = lane; i < v_dim; i += 32) {
+        const float z = to_float(gate[i]);
+        const float s = 1.f / (1.f + expf(-z));
+        dst[i] = from_float<T>(src[i] * r * w[i] * (act == 0 ? z * s : s));
+    }
+}
+
+cudaError_t launch_head_norm_gate(int dtype, const float* o, const void* y, int y_stride, int gate_col, const float* weight,
+                                  int weight_per_channel, float eps, int act, void* out, int out_stride, int out_col,
+                                  float out_scale, const int* token_seq, int n_tokens, int heads, int v_dim, cudaStream_t stream) {
+    const long long pairs = (long long)n_tokens * heads;
+    if (pairs == 0) return cudaSuccess;
+    const int blocks = (int)((pairs + 3) / 4);
+    if (dtype == kBF16)
+        return launch(head_norm_gate_kernel<__nv_bfloat16>, blocks, 128, 0, stream, o, (const __nv_bfloat16*)y, y_stride, gate_col,
+                      weight, weight_per_channel, eps, act, (__nv_bfloat16*)out, out_stride, out_col, out_scale, token_seq,
+                      n_tokens, heads, v_dim);
+    return launch(head_norm_gate_kernel<float>, blocks, 128, 0, stream, o, (const float*)y, y_stride, gate_col, weight,
+                  weight_per_channel, eps, act, (float*)out, out_stride, out_col, out_scale, token_seq, n_tokens, heads, v_dim);
+}
+
+}  // namespace vtb

@@ -113,13 +113,15 @@ def polynorm(z: torch.Tensor, coefficients: torch.Tensor, eps: float, out: torch
 
 
 def head_norm_gate(o: torch.Tensor, y: torch.Tensor, gate_col: int, weight: torch.Tensor, weight_per_channel: bool,
-                   eps: float, act: str, out: torch.Tensor, out_col: int, out_scale: float, heads: int, v_dim: int) -> torch.Tensor:
+                   eps: float, act: str, out: torch.Tensor, out_col: int, out_scale: float, heads: int, v_dim: int,
+                   token_seq: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out[t, out_col + h * v_dim + i] = out_scale * o[t, h, i] / sqrt(mean_i(o[t, h, :]^2) + eps) * w * act(gate)
     for the 32-bit o [T, heads * v_dim] of a recurrent mixer; gate = y[t, gate_col + h * v_dim + i]; w = weight[i]
     (a weight [v_dim] shared by the heads) or, with ``weight_per_channel``, weight[h * v_dim + i]; ``act`` is
-    "silu" or "sigmoid".  32-bit until the one rounding into ``out``."""
+    "silu" or "sigmoid".  32-bit until the one rounding into ``out``.  With ``token_seq`` (the step's sequence index
+    of every token) the rows of padding tokens (-1), for which nothing ran, become zero."""
     backend().head_norm_gate(o, y, int(gate_col), weight, bool(weight_per_channel), float(eps), _GATE_ACTS[act], out,
-                             int(out_col), float(out_scale), int(heads), int(v_dim))
+                             int(out_col), float(out_scale), int(heads), int(v_dim), token_seq)
     return out
 
 

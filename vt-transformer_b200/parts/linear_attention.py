@@ -67,7 +67,8 @@ class GatedLinearAttention(_Recurrent):
         o = torch.empty((y.shape[0], s.heads * s.v_dim), dtype=torch.float32, device=y.device)
         ops.gla_scan(y, cols[0], cols[1], cols[2], cols[4], self.a2, self.a2_bias, 1.0 / s.tau, s.dim ** -0.5,
                      cache.state, ctx, o, s.heads, s.dim, s.v_dim, status=ctx.status)
-        ops.head_norm_gate(o, y, cols[3], self.norm, False, s.norm_eps, "silu", out, out_col, out_scale, s.heads, s.v_dim)
+        ops.head_norm_gate(o, y, cols[3], self.norm, False, s.norm_eps, "silu", out, out_col, out_scale, s.heads, s.v_dim,
+                           token_seq=ctx.token_seq)
 
 
 @register_part("mixer", "delta_rule")
@@ -115,4 +116,5 @@ class DeltaRule(_Recurrent):
         o = torch.empty((y.shape[0], s.heads * s.dim), dtype=torch.float32, device=y.device)
         ops.delta_scan(y, cols[0], cols[1], cols[2], cols[4], cols[5], self.w2, self.w0, self.a_bias, s.decay_rate,
                        s.key_eps, cache.state, ctx, o, s.heads, s.dim, status=ctx.status)
-        ops.head_norm_gate(o, y, cols[3], self.norm, True, s.norm_eps, "sigmoid", out, out_col, out_scale, s.heads, s.dim)
+        ops.head_norm_gate(o, y, cols[3], self.norm, True, s.norm_eps, "sigmoid", out, out_col, out_scale, s.heads, s.dim,
+                           token_seq=ctx.token_seq)
