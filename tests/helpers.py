@@ -13,8 +13,7 @@ import torch
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
-# Three tiny configurations that differ in every size and option.  A and B are the two of the
-# task's description; C adds a window on the later layers, a head size that is no power of two,
+# Three tiny configurations that differ in every size and option.  A and B are the basic two; C adds a window on the later layers, a head size that is no power of two,
 # a head_dim that is not hidden / heads, and a vocabulary and width that are no powers of two.
 CONFIGS: Dict[str, dict] = {
     "A": dict(architectures=["Qwen2ForCausalLM"], vocab_size=256, hidden_size=64, intermediate_size=176,
@@ -104,7 +103,7 @@ _plain_cache: Dict[Tuple[str, Tuple[int, ...]], torch.Tensor] = {}
 
 def plain_logits(folder: str, tokens: Sequence[int]) -> torch.Tensor:
     """Logits [T, vocab] (float64) of the plain implementation for the whole sequence."""
-    from plain import qwen2_plain as plain
+    plain = plain_module(folder)
     key = (folder, tuple(tokens))
     if key not in _plain_cache:
         cfg, w = plain.read_config(folder), _plain_weights(folder)
@@ -112,13 +111,29 @@ def plain_logits(folder: str, tokens: Sequence[int]) -> torch.Tensor:
     return _plain_cache[key]
 
 
+def plain_module(folder: str):
+    """The plain implementation of the architecture that the folder's config.json names."""
+    with open(os.path.join(folder, "config.json")) as f:
+        c = json.load(f)
+    if c.get("architecture") == "Sisetar":
+        from plain import sisetar_plain
+        return sisetar_plain
+    from plain import qwen2_plain
+    return qwen2_plain
+
+
+def vocab_of(folder: str) -> int:
+    with open(os.path.join(folder, "config.json")) as f:
+        c = json.load(f)
+    return c["vocab_size"] if "vocab_size" in c else c["vocab"]
+
+
 _weights_cache: Dict[str, dict] = {}
 
 
 def _plain_weights(folder: str):
-    from plain import qwen2_plain as plain
     if folder not in _weights_cache:
-        _weights_cache[folder] = plain.read_weights(folder)
+        _weights_cache[folder] = plain_module(folder).read_weights(folder)
     return _weights_cache[folder]
 
 
@@ -238,7 +253,7 @@ def run_trace_cli(folder: str, trace: Trace, dtype: str, out_dir: str, max_token
     assert res.returncode == 0, f"trace_run failed ({res.returncode}):\n{res.stdout[-2000:]}\n{res.stderr[-4000:]}"
     done = [l for l in res.stdout.splitlines() if l.startswith("done ")]
     assert [int(l.split()[1]) for l in done] == [s["step"] for s in trace.steps], "a `done` line is missing"
-    vocab = json.load(open(os.path.join(folder, "config.json")))["vocab_size"]
+    vocab = vocab_of(folder)
     out = {}
     for n in trace.expect:
         arr = np.fromfile(os.path.join(out_dir, f"{n}.f32"), dtype="<f4")
