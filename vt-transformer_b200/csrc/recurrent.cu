@@ -218,8 +218,10 @@ cudaError_t launch_scan_kd(const ScanArgs& a, int n_seqs, cudaStream_t stream) {
     const size_t floats = ((a.dim * a.rank + 3) & ~3) + ((kScanTokens * a.rank + 3) & ~3)
                           + (size_t)(Delta ? 5 : 3) * kScanTokens * dim_p + kScanTokens * kScanCols + 2 * G * kScanCols;
     const size_t bytes = floats * sizeof(float);
-    if (bytes > 200 * 1024) return cudaErrorInvalidValue;
-    cudaError_t e = allow_dynamic_smem(scan_kernel<T, KD, Delta>, (int)bytes, done);
+    constexpr int kMostBytes = 200 * 1024;
+    if (bytes > kMostBytes) return cudaErrorInvalidValue;
+    // the limit is set once for each device, so it is the most any launch may ask for, not what this one asks for
+    cudaError_t e = allow_dynamic_smem(scan_kernel<T, KD, Delta>, kMostBytes, done);
     if (e != cudaSuccess) return e;
     dim3 grid(n_seqs, a.heads, (a.v_dim + kScanCols - 1) / kScanCols), block(kScanCols, G);
     return launch(scan_kernel<T, KD, Delta>, grid, block, bytes, stream, a);
