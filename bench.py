@@ -362,8 +362,155 @@ def other_points(pk, dev="cuda:0"):
     return out
 
 
+# ---- --design: a design's layers at sizes that resemble a served model's, beside the closest Qwen2 model of equal size ----
+
+def _sisetar_config(width, ff, gla, att, delta, chunk, pairs=2):
+    """``pairs`` times (a gated-linear-attention layer, a parallel layer with a feed-forward)."""
+    layers = []
+    for _ in range(pairs):
+        layers.append({"type": "gla", "mixer": {"heads": gla[0], "dim": gla[1], "vdim": gla[2], "tau": 16.0}, "mlp": None})
+        layers.append({"type": "parallel", "mixer": {
+            "left": {"heads": att[0], "kv_heads": att[1], "dim": att[2], "vdim": att[2], "rot": {"dims": att[2] // 2, "base": 1e6},
+                     "scale": att[2] ** -0.5, "mask": {"size": chunk}},
+            "right": {"heads": delta[0], "dim": delta[1]}, "left_scale": 1.0, "right_scale": 1.0},
+            "mlp": {"kind": "dense", "ff": ff}})
+    return {"architecture": "Sisetar", "vocab": 32768, "width": width, "layers": layers, "embedding": {"scale": 1.0},
+            "logit_scale": 1.0, "logit_softcap": 30.0, "norm": {"eps": 1e-6}}
+
+
+DESIGN_SIZES = {
+    # name: width, feed-forward, (gla heads, dim, vdim), (attention heads, kv heads, head size), (delta heads, dim), chunk
+    "w1024": (1024, 4096, (8, 64, 128), (16, 2, 64), (8, 64), 1024),
+    "w4096": (4096, 14336, (16, 128, 256), (32, 8, 128), (16, 128), 2048),
+}
+
+
+def design_points(design: str, sizes, steps: int, warmup: int) -> int:
+    """Prefill and decode throughput of ``design`` (random weights, bfloat16, pages of 64) at the sizes of
+    ``DESIGN_SIZES``, beside a Qwen2 model of the same width, layer count, feed-forward size and attention heads, and the
+    device time of every kernel of one prefill step and one decode step of each (eager, CUDA events around each call;
+    the steps that give the throughput run as they are served: prefill eager, decode as captured graphs)."""
+    if design != "sisetar":
+        print(f"bench.py: --design knows 'sisetar', not {design!r}")
+        return 2
+    import torch
+    from vt_transformer_b200 import ops
+    from vt_transformer_b200.config import config_from_dict
+    from vt_transformer_b200.engine import ModelRunner, StepEntry
+    dev, pk = "cuda:0", peaks()
+    gen = torch.Generator().manual_seed(4)
+    P, CTX, B_LIST = 4096, 1024, (8, 64)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)       # larger than L2: written between timed prefills
+    out = {"design": design, "dtype": "bf16", "data": "synthetic", "prefill_tokens": P, "decode_context": CTX,
+           "peaks": pk, "l2": "flushed between prefill steps; decode steps read weights and caches larger than L2 at w4096",
+           "sizes": {}}
+
+    def timed(fn, reps):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        for _ in range(reps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / reps
+
+    def per_kernel(runner, entries):
+        """Device time of each of the package's kernels in one eager step, by the name of the op."""
+        names = [n for n in ("embedding", "rmsnorm", "layernorm", "polynorm", "head_norm_gate", "gla_scan", "delta_scan",
+                             "attention_prepare", "attention_general", "rope_store", "paged_attention", "rope_attention", "linear",
+                             "linear_silu_mul", "linear_to_stream", "logits_scale_cap")]
+        saved, events = {n: getattr(ops, n) for n in names}, []
+
+        def wrap(name, fn):
+            def inner(*a, **k):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                r = fn(*a, **k)
+                e1.record()
+                events.append((name, e0, e1))
+                return r
+            return inner
+        for n in names:
+            setattr(ops, n, wrap(n, saved[n]))
+        graphs, runner.use_graphs = runner.use_graphs, False
+        try:
+            runner.step(entries)
+            torch.cuda.synchronize()
+        finally:
+            runner.use_graphs = graphs
+            for n in names:
+                setattr(ops, n, saved[n])
+        total = {}
+        nested = {"linear_to_stream", "linear_silu_mul", "rope_attention"}      # these call other ops of the list
+        for name, e0, e1 in events:
+            if name in nested:
+                continue
+            total[name] = total.get(name, 0.0) + e0.elapsed_time(e1) * 1e3
+        return {k: round(v, 1) for k, v in sorted(total.items())}
+
+    for size in sizes:
+        width, ff, gla, att, delta, chunk = DESIGN_SIZES[size]
+        vocab = 32768
+        models = {
+            "sisetar": _sisetar_config(width, ff, gla, att, delta, chunk),
+            "qwen2": dict(architectures=["Qwen2ForCausalLM"], vocab_size=vocab, hidden_size=width, intermediate_size=ff,
+                          num_hidden_layers=4, num_attention_heads=att[0], num_key_value_heads=att[1], head_dim=att[2],
+                          rms_norm_eps=1e-6, rope_theta=1e6, max_position_embeddings=8192, tie_word_embeddings=True),
+        }
+        res = {}
+        for name, raw in models.items():
+            cfg = config_from_dict(raw)
+            most = max(B_LIST)
+            runner = ModelRunner.from_random(cfg, seed=0, sigma=0.02, dtype="bfloat16", device=dev, page_size=PAGE,
+                                             num_pages=(most * (CTX + steps + warmup + 2 * PAGE) + P) // PAGE + 8,
+                                             max_requests=most, max_seq_len=8192)
+            toks = lambda n: torch.randint(0, vocab, (n,), generator=gen).tolist()
+            r = {"weight_bytes": runner.weight_bytes(1)}
+            prompt = toks(P)
+
+            def prefill():
+                flush.zero_()
+                row = runner.admit()
+                runner.step([StepEntry(row, prompt, [P - 1])])
+                runner.release(row)
+            for _ in range(max(3, warmup // 3)):
+                prefill()
+            flush_ms = timed(flush.zero_, 5)
+            ms = timed(prefill, 5) - flush_ms
+            r["prefill_ms"], r["prefill_tok_s"] = round(ms, 3), round(P / ms * 1e3, 1)
+            row = runner.admit()
+            r["prefill_kernels_us"] = per_kernel(runner, [StepEntry(row, prompt, [P - 1])])
+            runner.release(row)
+            for B in B_LIST:
+                rows = [runner.admit() for _ in range(B)]
+                for i in range(0, B, 4):
+                    runner.step([StepEntry(x, toks(CTX), []) for x in rows[i:i + 4]])
+                feed = toks(B)
+                one = lambda: runner.step([StepEntry(x, [feed[j]], [0]) for j, x in enumerate(rows)])
+                for _ in range(max(3, warmup)):
+                    one()
+                ms = timed(one, steps)
+                r[f"decode_b{B}_ms"], r[f"decode_b{B}_tok_s"] = round(ms, 4), round(B / ms * 1e3, 1)
+                r[f"decode_b{B}_hbm_fraction_of_{pk['source']}"] = round(runner.weight_bytes(B) / (ms * 1e-3) / (pk["hbm_gbs"] * 1e9), 3)
+                if B == max(B_LIST):
+                    r[f"decode_b{B}_kernels_us"] = per_kernel(runner, [StepEntry(x, [feed[j]], [0]) for j, x in enumerate(rows)])
+                for x in rows:
+                    runner.release(x)
+            runner.check_status()
+            res[name] = r
+            del runner
+            torch.cuda.empty_cache()
+        out["sizes"][size] = res
+    print(json.dumps(out))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
+    ap.add_argument("--design", default=None, help="instead of the default workload: prefill and decode throughput of this design "
+                    "('sisetar') at layer sizes that resemble a served model's, beside a Qwen2 model of equal size")
+    ap.add_argument("--design-sizes", default="w1024,w4096", help="which of the sizes of --design to run, with commas between them")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
@@ -379,6 +526,8 @@ def main() -> int:
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
+    if args.design:
+        return design_points(args.design, [x for x in args.design_sizes.split(",") if x], min(args.steps, 50), args.warmup)
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
