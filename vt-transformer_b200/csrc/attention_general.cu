@@ -109,7 +109,11 @@ cudaError_t launch_attention_prepare(int dtype, void* y, int stride, int q_col, 
                   table_stride, n_seqs, n_pages, heads, kv_heads, dim, v_dim, page_size, store, status);
 }
 
-template <typename T>
+// One warp for a (token, head).  The visible keys are taken 32 at a time, a lane a key: the lane forms its key's whole
+// score from q in shared memory (no exchange between lanes for a score), the block's maximum and sum are found once,
+// and the block's values are added with a lane owning dimensions i, i + 32, ... of the result.  The blocks start at the
+// first visible key, which depends on the token's position alone, so a token's result does not depend on the step.
+template <typename T, bool Vec>
 __global__ void __launch_bounds__(128)
 attention_general_kernel(const T* __restrict__ y, int stride, int q_col, T* __restrict__ out, int out_stride, int out_col,
                          float out_scale, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
@@ -117,10 +121,11 @@ attention_general_kernel(const T* __restrict__ y, int stride, int q_col, T* __re
                          const int* __restrict__ block_table, int table_stride, int n_seqs, int n_pages, int n_tokens,
                          int heads, int kv_heads, int dim, int v_dim, int page_size, int window, int chunk, float scale,
                          int* status) {
+    __shared__ __align__(16) float qs[4][32 * kMaxPerLane];
     pdl_launch();
     pdl_wait();
-    const int lane = threadIdx.x & 31;
-    const long long pair = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const long long pair = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
     if (pair >= (long long)n_tokens * heads) return;
     const int t = (int)(pair / heads), h = (int)(pair % heads);
     const int seq = token_seq[t];
@@ -136,44 +141,67 @@ attention_general_kernel(const T* __restrict__ y, int stride, int q_col, T* __re
     const int pos = positions[t];
     const int kvh = h / (heads / kv_heads);
     const int* table = block_table + (size_t)seq * table_stride;
-
-    float q[kMaxPerLane], acc[kMaxPerLane];
+    float* q = qs[warp];
     const T* qp = y + (size_t)t * stride + q_col + (size_t)h * dim;
+    for (int i = lane; i < dim; i += 32) q[i] = to_float(qp[i]) * scale;
+    __syncwarp();
+
+    float acc[kMaxPerLane];
 #pragma unroll
-    for (int r = 0; r < kMaxPerLane; ++r) {
-        const int i = lane + 32 * r;
-        q[r] = (i < dim) ? to_float(qp[i]) : 0.f;
-        acc[r] = 0.f;
-    }
+    for (int r = 0; r < kMaxPerLane; ++r) acc[r] = 0.f;
     float mx = -INFINITY, sum = 0.f;
     int first = (window > 0) ? max(0, pos - window + 1) : 0;
     if (chunk > 0) first = max(first, (pos / chunk) * chunk);      // chunks are counted from position 0 of the sequence
-    for (int j = first; j <= pos; ++j) {
-        const int page = table[j / page_size];
-        if (page < 0 || page >= n_pages) {
-            if (lane == 0) set_status(status, kStatusBadPage, page);
-            continue;
+    for (int j0 = first; j0 <= pos; j0 += 32) {
+        const int j = j0 + lane;
+        bool live = j <= pos;
+        int at = 0;                                                // the key's row in the pages
+        if (live) {
+            const int page = table[j / page_size];
+            if (page < 0 || page >= n_pages) {
+                set_status(status, kStatusBadPage, page);
+                live = false;
+            } else {
+                at = (page * kv_heads + kvh) * page_size + (j % page_size);
+            }
         }
-        const size_t at = ((size_t)page * kv_heads + kvh) * page_size + (j % page_size);
-        const T* kp = k_cache + at * dim;
-        float part = 0.f;
-#pragma unroll
-        for (int r = 0; r < kMaxPerLane; ++r) {
-            const int i = lane + 32 * r;
-            if (i < dim) part = fmaf(q[r], to_float(kp[i]), part);
+        float s = -INFINITY;
+        if (live) {
+            const T* kp = k_cache + (size_t)at * dim;
+            float part[4] = {0.f, 0.f, 0.f, 0.f};
+            if (Vec) {
+                for (int i = 0; i < dim; i += 8) {
+                    float k8[8];
+                    Vec8<T>::load(kp + i, k8);
+                    const float4 qa = *reinterpret_cast<const float4*>(q + i), qb = *reinterpret_cast<const float4*>(q + i + 4);
+                    part[0] = fmaf(qa.x, k8[0], part[0]); part[1] = fmaf(qa.y, k8[1], part[1]);
+                    part[2] = fmaf(qa.z, k8[2], part[2]); part[3] = fmaf(qa.w, k8[3], part[3]);
+                    part[0] = fmaf(qb.x, k8[4], part[0]); part[1] = fmaf(qb.y, k8[5], part[1]);
+                    part[2] = fmaf(qb.z, k8[6], part[2]); part[3] = fmaf(qb.w, k8[7], part[3]);
+                }
+            } else {
+                for (int i = 0; i < dim; ++i) part[i & 3] = fmaf(q[i], to_float(kp[i]), part[i & 3]);
+            }
+            s = (part[0] + part[1]) + (part[2] + part[3]);
         }
-        const float s = warp_sum(part) * scale;
-        const float new_mx = fmaxf(mx, s);
-        const float corr = expf(mx - new_mx);   // 0 at the first key (mx = -inf)
-        const float p = expf(s - new_mx);
-        sum = sum * corr + p;
-        const T* vp = v_cache + at * v_dim;
-#pragma unroll
-        for (int r = 0; r < kMaxPerLane; ++r) {
-            const int i = lane + 32 * r;
-            if (i < v_dim) acc[r] = acc[r] * corr + p * to_float(vp[i]);
-        }
+        const float new_mx = fmaxf(mx, warp_max(s));              // the first block holds the token's own key: finite
+        const float corr = expf(mx - new_mx);                      // 0 at the first block (mx = -inf)
+        const float p = live ? expf(s - new_mx) : 0.f;
+        sum = sum * corr + warp_sum(p);
         mx = new_mx;
+#pragma unroll
+        for (int r = 0; r < kMaxPerLane; ++r) acc[r] *= corr;
+        const int n = min(32, pos - j0 + 1);
+        for (int jj = 0; jj < n; ++jj) {
+            const float pj = __shfl_sync(0xffffffffu, p, jj);
+            const int aj = __shfl_sync(0xffffffffu, at, jj);
+            const T* vp = v_cache + (size_t)aj * v_dim;
+#pragma unroll
+            for (int r = 0; r < kMaxPerLane; ++r) {
+                const int i = lane + 32 * r;
+                if (i < v_dim) acc[r] = fmaf(pj, to_float(vp[i]), acc[r]);
+            }
+        }
     }
     const float inv = sum > 0.f ? out_scale / sum : 0.f;
 #pragma unroll
@@ -183,6 +211,22 @@ attention_general_kernel(const T* __restrict__ y, int stride, int q_col, T* __re
     }
 }
 
+template <typename T>
+static cudaError_t launch_attention_general_t(const T* y, int stride, int q_col, T* out, int out_stride, int out_col, float out_scale,
+                                              const T* k_cache, const T* v_cache, const int* positions, const int* token_seq,
+                                              const int* block_table, int table_stride, int n_seqs, int n_pages, int n_tokens,
+                                              int heads, int kv_heads, int dim, int v_dim, int page_size, int window, int chunk,
+                                              float scale, int* status, cudaStream_t stream) {
+    const long long pairs = (long long)n_tokens * heads;
+    const int blocks = (int)((pairs + 3) / 4);
+    // a key's row is read in 16-byte pieces where every row starts on such a boundary
+    const bool vec = dim % 8 == 0 && (reinterpret_cast<uintptr_t>(k_cache) & 15) == 0;
+    auto kernel = vec ? attention_general_kernel<T, true> : attention_general_kernel<T, false>;
+    return launch(kernel, blocks, 128, 0, stream, y, stride, q_col, out, out_stride, out_col, out_scale, k_cache, v_cache, positions,
+                  token_seq, block_table, table_stride, n_seqs, n_pages, n_tokens, heads, kv_heads, dim, v_dim, page_size, window,
+                  chunk, scale, status);
+}
+
 cudaError_t launch_attention_general(int dtype, const void* y, int stride, int q_col, void* out, int out_stride, int out_col,
                                      float out_scale, const void* k_cache, const void* v_cache, const int* positions,
                                      const int* token_seq, const int* block_table, int table_stride, int n_seqs, int n_pages,
@@ -190,17 +234,14 @@ cudaError_t launch_attention_general(int dtype, const void* y, int stride, int q
                                      int chunk, float scale, int* status, cudaStream_t stream) {
     if (n_tokens == 0) return cudaSuccess;
     if (dim > 32 * kMaxPerLane || v_dim > 32 * kMaxPerLane) return cudaErrorInvalidValue;
-    const long long pairs = (long long)n_tokens * heads;
-    const int blocks = (int)((pairs + 3) / 4);
     if (dtype == kBF16)
-        return launch(attention_general_kernel<__nv_bfloat16>, blocks, 128, 0, stream, (const __nv_bfloat16*)y, stride, q_col,
-                      (__nv_bfloat16*)out, out_stride, out_col, out_scale, (const __nv_bfloat16*)k_cache,
-                      (const __nv_bfloat16*)v_cache, positions, token_seq, block_table, table_stride, n_seqs, n_pages,
-                      n_tokens, heads, kv_heads, dim, v_dim, page_size, window, chunk, scale, status);
-    return launch(attention_general_kernel<float>, blocks, 128, 0, stream, (const float*)y, stride, q_col, (float*)out,
-                  out_stride, out_col, out_scale, (const float*)k_cache, (const float*)v_cache, positions, token_seq,
-                  block_table, table_stride, n_seqs, n_pages, n_tokens, heads, kv_heads, dim, v_dim, page_size, window,
-                  chunk, scale, status);
+        return launch_attention_general_t((const __nv_bfloat16*)y, stride, q_col, (__nv_bfloat16*)out, out_stride, out_col, out_scale,
+                                          (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, positions, token_seq,
+                                          block_table, table_stride, n_seqs, n_pages, n_tokens, heads, kv_heads, dim, v_dim,
+                                          page_size, window, chunk, scale, status, stream);
+    return launch_attention_general_t((const float*)y, stride, q_col, (float*)out, out_stride, out_col, out_scale, (const float*)k_cache,
+                                      (const float*)v_cache, positions, token_seq, block_table, table_stride, n_seqs, n_pages,
+                                      n_tokens, heads, kv_heads, dim, v_dim, page_size, window, chunk, scale, status, stream);
 }
 
 }  // namespace vtb

@@ -18,8 +18,9 @@ namespace vtb {
 
 namespace {
 
-constexpr int kScanCols = 32;     // columns of the state a CTA owns (one warp for each group of rows)
-constexpr int kScanTokens = 8;    // tokens staged in shared memory at once
+constexpr int kScanCols = 32;     // columns of the state a warp owns
+constexpr int kScanThreads = 256; // most threads of a CTA
+constexpr int kScanTokens = 16;   // tokens staged in shared memory at once
 
 struct ScanArgs {
     const void* y;                // [tokens, stride]: the projections
@@ -38,6 +39,7 @@ struct ScanArgs {
     const int* rows;              // [sequences]
     float* out;                   // [tokens, heads * v_dim]
     int heads, dim, v_dim, groups;
+    int col_blocks;               // warps of columns in a CTA
     int* status;
 };
 
@@ -48,40 +50,76 @@ __device__ __forceinline__ float log_sigmoid(float z) {
 
 __device__ __forceinline__ float sigmoid(float z) { return 1.f / (1.f + expf(-z)); }
 
+// A CTA owns `col_blocks` * 32 columns of one (sequence, head): thread (c, g, cb) keeps rows [g KD, (g + 1) KD) of column
+// (blockIdx.z col_blocks + cb) 32 + c in registers.  The step's tokens of the sequence are staged in batches of 16: all
+// threads fetch the batch's projections (independent loads, many in flight), form decay, removal rate and unit key
+// from them once for all columns, and then walk the batch's tokens out of shared memory.
 template <typename T, int KD, bool Delta>
-__global__ void __launch_bounds__(kScanCols * 8)
+__global__ void __launch_bounds__(kScanThreads, 1)
 scan_kernel(const ScanArgs a) {
     extern __shared__ __align__(16) float smem[];
     pdl_launch();
     const int seq = blockIdx.x, h = blockIdx.y;
-    const int c = threadIdx.x, g = threadIdx.y;
-    const int G = a.groups;
-    const int tid = g * kScanCols + c, n_threads = kScanCols * G;
+    const int c = threadIdx.x, g = threadIdx.y, cb = threadIdx.z;
+    const int G = a.groups, CB = a.col_blocks;
+    constexpr int TB = kScanTokens;
+    const int tid = (cb * G + g) * kScanCols + c, n_threads = kScanCols * G * CB;
     const int dim = a.dim, v_dim = a.v_dim, rank = a.rank;
-    const int dim_p = G * KD;
-    const int j = blockIdx.z * kScanCols + c;
+    const int dim_p = G * KD, cols = CB * kScanCols;
+    const int col0 = blockIdx.z * cols;
+    const int j = col0 + cb * kScanCols + c;
     const bool col_ok = j < v_dim;
+    constexpr int kVectors = Delta ? 3 : 2;                 // q (r), k and, for the delta rule, the removal rate
+    const int per = kVectors * dim_p + rank + cols;         // values of a token that the CTA reads
     // shared memory: the low-rank gate's second matrix for this head; a batch of tokens; the meeting place of the groups
-    float* w2s = smem;                                   // [dim, rank]
-    float* low = w2s + ((dim * rank + 3) & ~3);          // [tokens, rank]
-    float* qs = low + ((kScanTokens * rank + 3) & ~3);   // [tokens, dim_p] each:
-    float* ks = qs + kScanTokens * dim_p;
-    float* ds = ks + kScanTokens * dim_p;
-    float* us = ds + kScanTokens * dim_p;                // delta rule: the unit key
-    float* bs = us + (Delta ? kScanTokens * dim_p : 0);  // delta rule: removal rate times unit key
-    float* vs = bs + (Delta ? kScanTokens * dim_p : 0);  // [tokens, 32]
-    float* red = vs + kScanTokens * kScanCols;           // [2, G, 32]
+    float* w2s = smem;                                      // [dim, rank]
+    float* low = w2s + ((dim * rank + 3) & ~3);             // [tokens, rank]
+    float* qs = low + ((TB * rank + 3) & ~3);               // [tokens, dim_p] each:
+    float* ks = qs + TB * dim_p;
+    float* bs = ks + TB * dim_p;                            // delta rule: the removal rate, then that times the unit key
+    float* ds = bs + (Delta ? TB * dim_p : 0);              // the decay
+    float* us = ds + TB * dim_p;                            // delta rule: the unit key
+    float* vs = us + (Delta ? TB * dim_p : 0);              // [tokens, cols]
+    float* red = vs + TB * cols;                            // [2, CB, G, 32]
     // the weights are written by no kernel of the step: they are read before the wait
     for (int e = tid; e < dim * rank; e += n_threads) w2s[e] = a.w2[(size_t)h * dim * rank + e];
     pdl_wait();
     const int t0 = a.cu_q[seq], t1 = a.cu_q[seq + 1];
-    if (t1 <= t0) return;                                // a sequence without tokens in this step (padding): its state stays
+    if (t1 <= t0) return;                                   // a sequence without tokens in this step (padding): its state stays
     const int row = a.rows[seq];
     if (row < 0 || row >= a.state_rows) {
         if (tid == 0) set_status(a.status, kStatusBadRow, row);
         return;
     }
     const T* y = reinterpret_cast<const T*>(a.y);
+    // value r of a token: q, k, (removal rate), the gate's input, v
+    auto fetch = [&](const T* yr, int r) -> float {
+        if (r < kVectors * dim_p) {
+            const int which = r < dim_p ? 0 : (r < 2 * dim_p ? 1 : 2), i = r - which * dim_p;
+            if (i >= dim) return 0.f;
+            const int col = which == 0 ? a.q_col : (which == 1 ? a.k_col : a.a_col);
+            const float v = to_float(yr[col + h * dim + i]);
+            return (!Delta && which == 0) ? v * a.c2 : v;
+        }
+        r -= kVectors * dim_p;
+        if (r < rank) {
+            const float v = to_float(yr[a.low_col + r]);
+            return Delta ? tanhf(v) : v;
+        }
+        r -= rank;
+        return col0 + r < v_dim ? to_float(yr[a.v_col + h * v_dim + col0 + r]) : 0.f;
+    };
+    auto place = [&](int tb, int r, float v) {
+        if (r < kVectors * dim_p) {
+            const int which = r < dim_p ? 0 : (r < 2 * dim_p ? 1 : 2);
+            (which == 0 ? qs : (which == 1 ? ks : bs))[tb * dim_p + r - which * dim_p] = v;
+            return;
+        }
+        r -= kVectors * dim_p;
+        if (r < rank) { low[tb * rank + r] = v; return; }
+        vs[tb * cols + r - rank] = v;
+    };
+
     float* sp = a.state + (((size_t)row * a.heads + h) * dim) * v_dim;
     float S[KD];
 #pragma unroll
@@ -90,45 +128,37 @@ scan_kernel(const ScanArgs a) {
         S[i] = (col_ok && r < dim) ? sp[(size_t)r * v_dim + j] : 0.f;
     }
     int meet = 0;
-    for (int tb0 = t0; tb0 < t1; tb0 += kScanTokens) {
-        const int n = min(kScanTokens, t1 - tb0);
-        __syncthreads();                                 // the batch before is done with
-        for (int e = tid; e < n * rank; e += n_threads) {
-            const float v = to_float(y[(size_t)(tb0 + e / rank) * a.stride + a.low_col + e % rank]);
-            low[e] = Delta ? tanhf(v) : v;
-        }
-        for (int e = tid; e < n * kScanCols; e += n_threads) {
-            const int jj = blockIdx.z * kScanCols + e % kScanCols;
-            vs[e] = jj < v_dim ? to_float(y[(size_t)(tb0 + e / kScanCols) * a.stride + a.v_col + h * v_dim + jj]) : 0.f;
+    for (int tb0 = t0; tb0 < t1; tb0 += TB) {
+        const int n = min(TB, t1 - tb0);
+        __syncthreads();                                    // the batch before is done with
+#pragma unroll 4
+        for (int tb = 0; tb < n; ++tb) {
+            const T* yr = y + (size_t)(tb0 + tb) * a.stride;
+            for (int r = tid; r < per; r += n_threads) place(tb, r, fetch(yr, r));
         }
         __syncthreads();
         for (int e = tid; e < n * dim_p; e += n_threads) {
             const int tb = e / dim_p, i = e % dim_p;
-            float q = 0.f, k = 0.f, d = 0.f, b = 0.f;
+            float d = 0.f;
             if (i < dim) {
-                const T* yr = y + (size_t)(tb0 + tb) * a.stride;
                 const int ch = h * dim + i;
-                q = to_float(yr[a.q_col + ch]);
-                k = to_float(yr[a.k_col + ch]);
                 float z = a.bias2[ch];
                 const float* wr = w2s + i * rank;
                 const float* lr = low + tb * rank;
                 for (int r = 0; r < rank; ++r) z = fmaf(wr[r], lr[r], z);
                 if (Delta) {
                     d = expf(-a.c1 * sigmoid(z));
-                    b = sigmoid(to_float(yr[a.a_col + ch]) + a.a_bias[ch]);
+                    bs[e] = sigmoid(bs[e] + a.a_bias[ch]);
                 } else {
                     d = expf(a.c1 * log_sigmoid(z));
-                    q *= a.c2;
                 }
             }
-            qs[e] = q; ks[e] = k; ds[e] = d;
-            if (Delta) bs[e] = b;
+            ds[e] = d;
         }
         __syncthreads();
         if (Delta) {
             // the unit key u = k / sqrt(sum(k^2) + eps), and b = a * u: a warp for each staged token
-            for (int tb = g; tb < n; tb += G) {
+            for (int tb = cb * G + g; tb < n; tb += G * CB) {
                 float ss = 0.f;
                 for (int i = c; i < dim_p; i += 32) ss = fmaf(ks[tb * dim_p + i], ks[tb * dim_p + i], ss);
                 ss = warp_sum(ss);
@@ -142,7 +172,7 @@ scan_kernel(const ScanArgs a) {
             __syncthreads();
         }
         for (int tb = 0; tb < n; ++tb) {
-            const float v = vs[tb * kScanCols + c];
+            const float v = vs[tb * cols + cb * kScanCols + c];
             const float4* q4 = reinterpret_cast<const float4*>(qs + tb * dim_p + g * KD);
             const float4* k4 = reinterpret_cast<const float4*>(ks + tb * dim_p + g * KD);
             const float4* d4 = reinterpret_cast<const float4*>(ds + tb * dim_p + g * KD);
@@ -161,7 +191,7 @@ scan_kernel(const ScanArgs a) {
                 }
                 float us_old = (part[0] + part[1]) + (part[2] + part[3]);
                 if (G > 1) {
-                    float* m = red + (meet++ & 1) * G * kScanCols;
+                    float* m = red + ((meet++ & 1) * CB + cb) * G * kScanCols;
                     m[g * kScanCols + c] = us_old;
                     __syncthreads();
                     us_old = 0.f;
@@ -195,7 +225,7 @@ scan_kernel(const ScanArgs a) {
             }
             float o = (acc[0] + acc[1]) + (acc[2] + acc[3]);
             if (G > 1) {
-                float* m = red + (meet++ & 1) * G * kScanCols;
+                float* m = red + ((meet++ & 1) * CB + cb) * G * kScanCols;
                 m[g * kScanCols + c] = o;
                 __syncthreads();
                 o = 0.f;
@@ -212,18 +242,24 @@ scan_kernel(const ScanArgs a) {
 }
 
 template <typename T, int KD, bool Delta>
-cudaError_t launch_scan_kd(const ScanArgs& a, int n_seqs, cudaStream_t stream) {
+cudaError_t launch_scan_kd(ScanArgs a, int n_seqs, cudaStream_t stream) {
     static std::atomic<unsigned long long> done{0};
     const int G = a.groups, dim_p = G * KD;
+    // as many warps of columns a CTA as the head has, within the CTA's threads
+    const int col_warps = (a.v_dim + kScanCols - 1) / kScanCols;
+    const int most = max(1, kScanThreads / (kScanCols * G));
+    const int ctas = (col_warps + most - 1) / most;                       // CTAs a head, with its warps of columns spread evenly
+    a.col_blocks = (col_warps + ctas - 1) / ctas;
+    const int cols = a.col_blocks * kScanCols;
     const size_t floats = ((a.dim * a.rank + 3) & ~3) + ((kScanTokens * a.rank + 3) & ~3)
-                          + (size_t)(Delta ? 5 : 3) * kScanTokens * dim_p + kScanTokens * kScanCols + 2 * G * kScanCols;
+                          + (size_t)(Delta ? 5 : 3) * kScanTokens * dim_p + kScanTokens * cols + 2 * a.col_blocks * G * kScanCols;
     const size_t bytes = floats * sizeof(float);
     constexpr int kMostBytes = 200 * 1024;
     if (bytes > kMostBytes) return cudaErrorInvalidValue;
     // the limit is set once for each device, so it is the most any launch may ask for, not what this one asks for
     cudaError_t e = allow_dynamic_smem(scan_kernel<T, KD, Delta>, kMostBytes, done);
     if (e != cudaSuccess) return e;
-    dim3 grid(n_seqs, a.heads, (a.v_dim + kScanCols - 1) / kScanCols), block(kScanCols, G);
+    dim3 grid(n_seqs, a.heads, (col_warps + a.col_blocks - 1) / a.col_blocks), block(kScanCols, G, a.col_blocks);
     return launch(scan_kernel<T, KD, Delta>, grid, block, bytes, stream, a);
 }
 
@@ -245,7 +281,7 @@ cudaError_t launch_gla_scan(int dtype, const void* y, int stride, int q_col, int
                             int v_dim, int* status, cudaStream_t stream) {
     if (n_seqs == 0) return cudaSuccess;
     ScanArgs a = {y, stride, q_col, k_col, v_col, 0, low_col, rank, a2, a2_bias, nullptr, inv_tau, q_scale, state,
-                  state_rows, cu_q, rows, out, heads, dim, v_dim, 1, status};
+                  state_rows, cu_q, rows, out, heads, dim, v_dim, 1, 1, status};
     return dtype == kBF16 ? launch_scan_t<__nv_bfloat16, false>(a, n_seqs, stream) : launch_scan_t<float, false>(a, n_seqs, stream);
 }
 
@@ -255,7 +291,7 @@ cudaError_t launch_delta_scan(int dtype, const void* y, int stride, int r_col, i
                               float* out, int heads, int dim, int* status, cudaStream_t stream) {
     if (n_seqs == 0) return cudaSuccess;
     ScanArgs a = {y, stride, r_col, k_col, v_col, a_col, low_col, rank, w2, w0, a_bias, decay_rate, key_eps, state,
-                  state_rows, cu_q, rows, out, heads, dim, dim, 1, status};
+                  state_rows, cu_q, rows, out, heads, dim, dim, 1, 1, status};
     return dtype == kBF16 ? launch_scan_t<__nv_bfloat16, true>(a, n_seqs, stream) : launch_scan_t<float, true>(a, n_seqs, stream);
 }
 
