@@ -45,16 +45,21 @@ CONFIGS: Dict[str, dict] = {
                   emb=3.0, logit_scale=0.7, cap=8.0),
     "wide": _model(257, 72, [_gla(2, 136, 72, 8.0), _par(2, 1, 72, 20, 0, 10000.0, 0.2, 50, 1, 160, 1.5, 0.6, ff=40),
                              _gla(1, 72, 100, 2.0)], emb=1.0, logit_scale=1.0, cap=0.0, eps=1e-6),
+    # values as wide as keys at head sizes that the tensor-core attention kernels take (32: mma.sync tiles and the
+    # single-token kernel; 64 with four query heads a group: tcgen05 for portions of 32 tokens and more)
+    "square": _model(200, 64, [_par(4, 2, 32, 32, 16, 1000.0, 0.2, 21, 1, 24, 1.3, 0.7, ff=48), _gla(2, 16, 16, 2.0)], emb=2.0, cap=6.0),
+    "square64": _model(200, 64, [_par(4, 1, 64, 64, 64, 1e4, 0.125, 100, 1, 16, 1.0, 1.0)], emb=2.0),
     "gla_only": _model(128, 48, [_gla(2, 20, 28, 3.0), _gla(2, 20, 28, 3.0, ff=56)], emb=2.0, cap=5.0),
     "gla_alone": _model(128, 48, [_gla(3, 16, 24, 2.0)], emb=2.0),
     "attention_alone": _model(128, 48, [_par(3, 1, 24, 40, 12, 777.0, 0.25, 9, 1, 8, 1.0, 0.0)], emb=2.0),
     "delta_alone": _model(128, 48, [_par(1, 1, 8, 8, 4, 777.0, 0.25, 9, 2, 36, 0.0, 1.0)], emb=2.0),
     "ffn_alone": _model(128, 48, [_gla(1, 8, 8, 2.0, ff=88)], emb=2.0),
 }
-SIGMA = {"mix": 0.15, "wide": 0.12, "gla_only": 0.2, "gla_alone": 0.2, "attention_alone": 0.25, "delta_alone": 0.2,
+SIGMA = {"mix": 0.15, "wide": 0.12, "square": 0.2, "square64": 0.2, "gla_only": 0.2, "gla_alone": 0.2, "attention_alone": 0.25, "delta_alone": 0.2,
          "ffn_alone": 0.2}
 SEED = {n: 100 + i for i, n in enumerate(CONFIGS)}
-LENGTHS = {"mix": [1, 9, 40, 71, 130], "wide": [3, 33, 90, 52], "gla_only": [2, 30, 77]}
+LENGTHS = {"mix": [1, 9, 40, 71, 130], "wide": [3, 33, 90, 52], "gla_only": [2, 30, 77], "square": [1, 19, 64, 110],
+           "square64": [5, 150, 260, 64]}
 
 
 def make_folder(name: str, folder: str) -> str:

@@ -86,6 +86,41 @@ def test_cuts_equal_the_plain_implementation(sisetar_folders, name, family, dtyp
     cases.replay(sisetar_folders(name), cases.prompts_for(name), family, DEV, dtype)
 
 
+@pytest.mark.parametrize("family", ["whole", "tail", "portions", "mixed"])
+@pytest.mark.parametrize("name", ["square", "square64"])
+def test_chunks_through_the_tensor_core_attention_kernels(sisetar_folders, name, family):
+    """Values as wide as keys: in bfloat16 the attention runs the kernels of the plain attention with the chunk as one
+    more bound of the keys (32-bit runs the general kernel: the same cases, as the oracle's check of the configuration)."""
+    from vt_transformer_b200 import ops
+    folder = sisetar_folders(name)
+    before = ops.launches
+    cases.replay(folder, cases.prompts_for(name), family, DEV, "bfloat16", sizes=(40, 3, 64, 2, 150))
+    cases.replay(folder, cases.prompts_for(name), family, DEV, "float32", sizes=(40, 3, 64, 2, 150))
+    assert ops.launches > before
+
+
+def test_keys_at_a_chunks_edge_through_the_tensor_core_kernels(sisetar_folders, tmp_path):
+    """The marked token just inside and just outside the asking position's chunk of 100, where a tile of 128 rows and a
+    block of 128 keys straddle the chunk's edge; prompt portions (tcgen05, mma.sync) and single tokens."""
+    folder = cases.rewritten(sisetar_folders("square64"), str(tmp_path / "sharp64"), lambda t: cases.sharpen_attention(t, 6.0))
+    base = cases.prompts_for("square64", lengths=[330])[0]
+    ask, start = 317, 300
+    marked = max(range(0, 200, 7), key=lambda tok: _sensitivity(folder, base, ask, start, tok))
+    runner = cases.runner_for(folder, DEV, "bfloat16", num_pages=24, max_requests=1)
+    seen = {}
+    for where in (start, start - 1):
+        ids = list(base)
+        ids[where] = marked
+        ref = _logits(folder, ids)
+        seen[where] = ref[ask]
+        for cuts in ([len(ids)], [ask, 1, 1, 1], [150, 149, 1, 1, 16], [299, 31]):
+            row = runner.admit()
+            got = cases.step_all(runner, row, ids, cuts)
+            runner.release(row)
+            assert float((got - ref).abs().max()) <= cases.tol("bfloat16", ref), (where, cuts)
+    assert float((seen[start] - seen[start - 1]).abs().max()) > 3 * cases.tol("bfloat16", _logits(folder, base))
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_portions_of_two_tokens_and_pages_of_64(sisetar_folders, dtype):
     folder = sisetar_folders("mix")

@@ -12,7 +12,7 @@ cudaError_t launch_attention_decode(const void* qkv, int qkv_stride, void* out, 
                                     int page_size, int window, float scale, int n_splits, float* part_o, float* part_ml,
                                     int* counters, int fuse_rope, const float2* cos_sin, int max_pos, int store_kv,
                                     const float* qkv_shares, int n_shares, int long_runs, int run_blocks, int* status,
-                                    cudaStream_t stream) {
+                                    cudaStream_t stream, int chunk) {
     if (n_seqs == 0 || n_tokens == 0) return cudaSuccess;
     if (!attention_mma_supports(head_dim, heads, kv_heads, 1) || page_size % 16 != 0) return cudaErrorInvalidValue;
     if (n_splits < 1) n_splits = 1;
@@ -39,6 +39,7 @@ cudaError_t launch_attention_decode(const void* qkv, int qkv_stride, void* out, 
     p.kv_heads = kv_heads;
     p.page_size = page_size;
     p.window = window;
+    p.chunk = chunk;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.tokens_per_tile = fuse_rope ? 1 : 16 / (heads / kv_heads);
     p.run_keys = long_runs ? 1 : 0;                  // the launcher of a head size with boxes sets the rows of a box

@@ -93,7 +93,7 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters, const __
     const int rows_valid = ntok * group;
     const int start = p.q_start[seq];
     const int pos_lo = start, pos_hi = start + ntok - 1;
-    int key_lo = (p.window > 0) ? max(0, pos_lo - p.window + 1) : 0;
+    int key_lo = first_visible_key(pos_lo, p.window, p.chunk);
     key_lo = key_lo / DKB * DKB;
     const int key_hi = pos_hi + 1;
     const int nblk = (key_hi - key_lo + DKB - 1) / DKB;
@@ -447,7 +447,7 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters, const __
             float mnew[2] = {mrow[0], mrow[1]};
             // a block all of whose keys every token sees needs no comparison of positions (rows beyond the valid
             // ones hold q = 0 and are never stored: they may run along)
-            const bool open = (kb + DKB - 1 <= pos_lo) && (p.window <= 0 || kb > pos_hi - p.window);
+            const bool open = (kb + DKB - 1 <= pos_lo) && kb >= first_visible_key(pos_hi, p.window, p.chunk);
             if (open) {
 #pragma unroll
                 for (int kt = 0; kt < DKB / 16; ++kt) {
@@ -464,7 +464,7 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters, const __
                     for (int e = 0; e < 4; ++e) {
                         const int c = e & 1;
                         const int key = kb + kt * 16 + gq + (e >> 1) * 8;
-                        const bool see = nvalid[c] && key <= npos[c] && (p.window <= 0 || key > npos[c] - p.window);
+                        const bool see = nvalid[c] && key <= npos[c] && key >= first_visible_key(npos[c], p.window, p.chunk);
                         st[kt][e] = see ? st[kt][e] * p.scale_log2 : -INFINITY;
                         mnew[c] = fmaxf(mnew[c], st[kt][e]);
                     }
@@ -529,7 +529,7 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters, const __
             }
             float mnew[2] = {mrow[0], mrow[1]};
             // a block all of whose keys every token of the tile sees needs no comparison of positions
-            const bool open = (kb + DKB - 1 <= pos_lo) && (p.window <= 0 || kb > pos_hi - p.window);
+            const bool open = (kb + DKB - 1 <= pos_lo) && kb >= first_visible_key(pos_hi, p.window, p.chunk);
             if (open) {
 #pragma unroll
                 for (int j = 0; j < DKB / 8; ++j) {
@@ -546,7 +546,7 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters, const __
                     for (int e = 0; e < 4; ++e) {
                         const int i = e >> 1;
                         const int key = kb + j * 8 + 2 * tq + (e & 1);
-                        const bool see = valid[i] && key <= pos[i] && (p.window <= 0 || key > pos[i] - p.window);
+                        const bool see = valid[i] && key <= pos[i] && key >= first_visible_key(pos[i], p.window, p.chunk);
                         s[j][e] = see ? s[j][e] * p.scale_log2 : -INFINITY;
                         mnew[i] = fmaxf(mnew[i], s[j][e]);
                     }

@@ -56,7 +56,7 @@ attention_mma_kernel(const AttnParams p) {
     const int rows_valid = ntok * group;
     const int start = p.q_start[seq];
     const int pos_lo = start + tok0, pos_hi = pos_lo + ntok - 1;
-    int key_lo = (p.window > 0) ? max(0, pos_lo - p.window + 1) : 0;
+    int key_lo = first_visible_key(pos_lo, p.window, p.chunk);
     key_lo = key_lo / KB * KB;
     const int key_hi = pos_hi + 1;
     const int nblk = (key_hi - key_lo + KB - 1) / KB;
@@ -162,7 +162,7 @@ attention_mma_kernel(const AttnParams p) {
         // mask, running maximum and sum (log2 domain)
         float mnew[2] = {mrow[0], mrow[1]};
         // a block all of whose keys every row of the tile sees needs no mask
-        const bool open = (kb + KB - 1 <= pos_lo) && (p.window <= 0 || kb > pos_hi - p.window);
+        const bool open = (kb + KB - 1 <= pos_lo) && kb >= first_visible_key(pos_hi, p.window, p.chunk);
         if (open) {
 #pragma unroll
             for (int j = 0; j < KB / 8; ++j) {
@@ -179,7 +179,7 @@ attention_mma_kernel(const AttnParams p) {
                 for (int e = 0; e < 4; ++e) {
                     const int i = e >> 1;
                     const int key = kb + j * 8 + 2 * tq + (e & 1);
-                    const bool see = valid[i] && key <= pos[i] && (p.window <= 0 || key > pos[i] - p.window);
+                    const bool see = valid[i] && key <= pos[i] && key >= first_visible_key(pos[i], p.window, p.chunk);
                     s[j][e] = see ? s[j][e] * p.scale_log2 : -INFINITY;
                     mnew[i] = fmaxf(mnew[i], s[j][e]);
                 }
@@ -342,7 +342,7 @@ cudaError_t launch_attention_mma(const void* qkv, int qkv_stride, void* out, con
                                  const int* cu_q, const int* q_start, const int* block_table, int table_stride,
                                  const int* tiles, int n_tiles, int n_pages, int n_tokens, int heads, int kv_heads,
                                  int head_dim, int page_size, int window, float scale, int warps, int n_splits,
-                                 float* part_o, float* part_ml, int* status, cudaStream_t stream) {
+                                 float* part_o, float* part_ml, int* status, cudaStream_t stream, int chunk) {
     if (n_tiles == 0 || n_tokens == 0) return cudaSuccess;
     if (!attention_mma_supports(head_dim, heads, kv_heads, warps) || page_size % 16 != 0) return cudaErrorInvalidValue;
     if (n_splits > 1 && (part_o == nullptr || part_ml == nullptr)) return cudaErrorInvalidValue;
@@ -371,6 +371,7 @@ cudaError_t launch_attention_mma(const void* qkv, int qkv_stride, void* out, con
     p.kv_heads = kv_heads;
     p.page_size = page_size;
     p.window = window;
+    p.chunk = chunk;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.tokens_per_tile = (16 * warps) / (heads / kv_heads);
     p.n_splits = n_splits < 1 ? 1 : n_splits;

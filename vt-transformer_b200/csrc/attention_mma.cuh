@@ -22,7 +22,7 @@ struct AttnParams {
     const int* block_table;
     int table_stride;
     const int2* tiles;      // (sequence, first token of the tile among the sequence's new tokens); null: tile = sequence
-    int n_pages, heads, kv_heads, page_size, window;
+    int n_pages, heads, kv_heads, page_size, window, chunk;
     float scale_log2;       // scale * log2(e)
     int tokens_per_tile;
     int run_keys;              // single-token steps, head sizes 64 and 128: rows of a box of the keys' and values' tensor maps

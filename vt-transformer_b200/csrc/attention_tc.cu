@@ -53,7 +53,7 @@ struct AttnTcParams {
     const int* block_table;
     int table_stride;
     const int2* tiles;
-    int n_pages, heads, kv_heads, page_size, window;
+    int n_pages, heads, kv_heads, page_size, window, chunk;
     float scale_log2;
     int tokens_per_tile;
     int run_keys;            // keys of a run: 16, 32, 64 or 128, a divisor of the page size
@@ -171,7 +171,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     const int rows_valid = max(0, ntok) * group;
     const int start = p.q_start[seq];
     const int pos_lo = start + tok0, pos_hi = pos_lo + max(1, ntok) - 1;
-    int key_lo = (p.window > 0) ? max(0, pos_lo - p.window + 1) : 0;
+    int key_lo = first_visible_key(pos_lo, p.window, p.chunk);
     key_lo = key_lo / TK * TK;
     const int key_hi = pos_hi + 1;
     const int nb = (ntok > 0) ? (key_hi - key_lo + TK - 1) / TK : 0;
@@ -327,12 +327,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
             tc_fence_after();
             const int kb = key_lo + j * TK;
             // a block all of whose keys every row of the tile sees needs no mask
-            const bool open = (kb + TK - 1 <= pos_lo) && (p.window <= 0 || kb > pos_hi - p.window);
+            const bool open = (kb + TK - 1 <= pos_lo) && kb >= first_visible_key(pos_hi, p.window, p.chunk);
             uint32_t raw[TK];
             load_row(s_addr, raw);
             // keys [lo, hi) of the block are seen by this row
             const int hi = valid ? pos - kb + 1 : 0;
-            const int lo = (p.window > 0) ? pos - p.window + 1 - kb : 0;
+            const int lo = first_visible_key(pos, p.window, p.chunk) - kb;
             const float raw_max = open ? row_max<false>(raw, lo, hi) : row_max<true>(raw, lo, hi);
             const float mx = fmaxf(m, raw_max * p.scale_log2);          // the scale is positive
             // a row that has seen no key yet takes the maximum as it is: its O is still zero
@@ -450,7 +450,7 @@ bool attention_tc_supports(int head_dim, int heads, int kv_heads) {
 cudaError_t launch_attention_tc(const void* qkv, int qkv_stride, void* out, const void* k_cache, const void* v_cache,
                                 const int* cu_q, const int* q_start, const int* block_table, int table_stride,
                                 const int* tiles, int n_tiles, int n_pages, int heads, int kv_heads, int head_dim,
-                                int page_size, int window, float scale, int* status, cudaStream_t stream) {
+                                int page_size, int window, float scale, int* status, cudaStream_t stream, int chunk) {
     if (n_tiles == 0) return cudaSuccess;
     if (!attention_tc_supports(head_dim, heads, kv_heads) || page_size % 16 != 0 || tiles == nullptr) return cudaErrorInvalidValue;
     const long long cache_rows = (long long)n_pages * kv_heads * page_size;
@@ -473,6 +473,7 @@ cudaError_t launch_attention_tc(const void* qkv, int qkv_stride, void* out, cons
     p.kv_heads = kv_heads;
     p.page_size = page_size;
     p.window = window;
+    p.chunk = chunk;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.tokens_per_tile = TQ / (heads / kv_heads);
     p.cache_rows = (int)cache_rows;

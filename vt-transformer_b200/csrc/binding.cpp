@@ -147,6 +147,16 @@ void head_norm_gate(const Tensor& o, const Tensor& y, int64_t gate_col, const Te
                                             o.size(0), heads, v_dim, stream_of(o)), "head_norm_gate");
 }
 
+void scale_into(const Tensor& src, Tensor& dst, int64_t dst_col, double scale) {
+    check_cuda(src, "src"); check_cuda(dst, "dst");
+    TORCH_CHECK(src.dim() == 2 && dst.dim() == 2 && src.size(0) == dst.size(0) && src.scalar_type() == dst.scalar_type(),
+                "scale_into: src [tokens, n] and dst [tokens, stride] of one dtype");
+    check_cols(dst, dst_col, src.size(1), "scale_into");
+    c10::cuda::CUDAGuard guard(src.device());
+    check_launch(vtb::launch_scale_into(dtype_code(src, "src"), src.data_ptr(), dst.data_ptr(), src.size(0), src.size(1), dst.size(1),
+                                        dst_col, (float)scale, stream_of(src)), "scale_into");
+}
+
 void check_scan(const Tensor& y, const Tensor& state, const Tensor& cu_q, const Tensor& rows, const Tensor& o, int64_t heads, int64_t dim,
                 int64_t v_dim, const char* who) {
     check_cuda(y, "y"); check_f32(state, "state"); check_i32(cu_q, "cu_q"); check_i32(rows, "rows"); check_f32(o, "o");
@@ -245,6 +255,8 @@ void attention_general(const Tensor& y, int64_t q_col, Tensor& out, int64_t out_
                                                window, chunk, (float)scale, status_ptr(status), stream_of(y)), "attention_general");
 }
 
+
+void scale_into(const Tensor& src, Tensor& dst, int64_t dst_col, double scale);
 
 void silu_mul(const Tensor& gu, Tensor& out, int64_t interleave) {
     check_cuda(gu, "gu"); check_cuda(out, "out");
@@ -441,7 +453,7 @@ bool attention_mma_supports(int64_t head_dim, int64_t heads, int64_t kv_heads, i
 void attention_mma(const Tensor& qkv, Tensor& out, const Tensor& k_cache, const Tensor& v_cache, const Tensor& cu_q,
                    const Tensor& q_start, const Tensor& block_table, c10::optional<Tensor> tiles, int64_t heads,
                    int64_t kv_heads, int64_t head_dim, int64_t window, double scale, int64_t warps, int64_t n_splits,
-                   c10::optional<Tensor> part_o, c10::optional<Tensor> part_ml, c10::optional<Tensor> status) {
+                   c10::optional<Tensor> part_o, c10::optional<Tensor> part_ml, c10::optional<Tensor> status, int64_t chunk) {
     check_cuda(qkv, "qkv"); check_cuda(out, "out"); check_i32(cu_q, "cu_q"); check_i32(q_start, "q_start");
     check_i32(block_table, "block_table");
     TORCH_CHECK(qkv.scalar_type() == torch::kBFloat16 && out.scalar_type() == torch::kBFloat16,
@@ -481,7 +493,7 @@ void attention_mma(const Tensor& qkv, Tensor& out, const Tensor& k_cache, const 
                                            v_cache.data_ptr(), cu_q.data_ptr<int>(), q_start.data_ptr<int>(),
                                            block_table.data_ptr<int>(), block_table.size(1), tp, n_tiles,
                                            k_cache.size(0), n_tokens, heads, kv_heads, head_dim, k_cache.size(2), window,
-                                           (float)scale, warps, n_splits, po, pm, status_ptr(status), stream_of(qkv)),
+                                           (float)scale, warps, n_splits, po, pm, status_ptr(status), stream_of(qkv), (int)chunk),
                  "attention_mma");
 }
 
@@ -491,7 +503,7 @@ bool attention_tc_supports(int64_t head_dim, int64_t heads, int64_t kv_heads) {
 
 void attention_tc(const Tensor& qkv, Tensor& out, const Tensor& k_cache, const Tensor& v_cache, const Tensor& cu_q,
                   const Tensor& q_start, const Tensor& block_table, const Tensor& tiles, int64_t heads, int64_t kv_heads,
-                  int64_t head_dim, int64_t window, double scale, c10::optional<Tensor> status) {
+                  int64_t head_dim, int64_t window, double scale, c10::optional<Tensor> status, int64_t chunk) {
     check_cuda(qkv, "qkv"); check_cuda(out, "out"); check_i32(cu_q, "cu_q"); check_i32(q_start, "q_start");
     check_i32(block_table, "block_table"); check_i32(tiles, "tiles");
     TORCH_CHECK(qkv.scalar_type() == torch::kBFloat16 && out.scalar_type() == torch::kBFloat16,
@@ -518,7 +530,7 @@ void attention_tc(const Tensor& qkv, Tensor& out, const Tensor& k_cache, const T
                                           v_cache.data_ptr(), cu_q.data_ptr<int>(), q_start.data_ptr<int>(),
                                           block_table.data_ptr<int>(), block_table.size(1), tiles.data_ptr<int>(),
                                           tiles.size(0), k_cache.size(0), heads, kv_heads, head_dim, k_cache.size(2),
-                                          window, (float)scale, status_ptr(status), stream_of(qkv)),
+                                          window, (float)scale, status_ptr(status), stream_of(qkv), (int)chunk),
                  "attention_tc");
 }
 
@@ -527,7 +539,7 @@ void attention_decode(const Tensor& qkv, Tensor& out, const Tensor& k_cache, con
                       int64_t window, double scale, int64_t n_splits, c10::optional<Tensor> part_o,
                       c10::optional<Tensor> part_ml, c10::optional<Tensor> counters, bool fuse_rope,
                       c10::optional<Tensor> cos_sin, bool store_kv, c10::optional<Tensor> status,
-                      c10::optional<Tensor> qkv_shares, bool long_runs, int64_t run_blocks) {
+                      c10::optional<Tensor> qkv_shares, bool long_runs, int64_t run_blocks, int64_t chunk) {
     check_cuda(qkv, "qkv"); check_cuda(out, "out"); check_i32(cu_q, "cu_q"); check_i32(q_start, "q_start");
     check_i32(block_table, "block_table");
     TORCH_CHECK(qkv.scalar_type() == torch::kBFloat16 && out.scalar_type() == torch::kBFloat16,
@@ -586,7 +598,7 @@ void attention_decode(const Tensor& qkv, Tensor& out, const Tensor& k_cache, con
                                               n_tokens, heads, kv_heads, head_dim, k_cache.size(2), window, (float)scale,
                                               n_splits, po, pm, pc, fuse_rope ? 1 : 0, cs, max_pos, store_kv ? 1 : 0,
                                               shp, n_shares, long_runs ? 1 : 0, (int)run_blocks, status_ptr(status),
-                                              stream_of(qkv)), "attention_decode");
+                                              stream_of(qkv), (int)chunk), "attention_decode");
 }
 
 void attention_simt(const Tensor& qkv, Tensor& out, const Tensor& k_cache, const Tensor& v_cache,
@@ -646,6 +658,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("layernorm", &layernorm, py::arg("x"), py::arg("delta"), py::arg("weight"), py::arg("eps"), py::arg("out"),
           py::arg("rows") = py::none(), py::arg("status") = py::none());
     m.def("polynorm", &polynorm);
+    m.def("scale_into", &scale_into);
     m.def("head_norm_gate", &head_norm_gate, py::arg("o"), py::arg("y"), py::arg("gate_col"), py::arg("weight"),
           py::arg("weight_per_channel"), py::arg("eps"), py::arg("act"), py::arg("out"), py::arg("out_col"), py::arg("out_scale"),
           py::arg("heads"), py::arg("v_dim"), py::arg("token_seq") = py::none());
@@ -673,17 +686,19 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("cu_q"), py::arg("q_start"), py::arg("block_table"), py::arg("tiles"), py::arg("heads"),
           py::arg("kv_heads"), py::arg("head_dim"), py::arg("window"), py::arg("scale"), py::arg("warps"),
           py::arg("n_splits"), py::arg("part_o") = py::none(), py::arg("part_ml") = py::none(),
-          py::arg("status") = py::none());
+          py::arg("status") = py::none(), py::arg("chunk") = 0);
     m.def("attention_tc_supports", &attention_tc_supports);
     m.def("attention_tc", &attention_tc, py::arg("qkv"), py::arg("out"), py::arg("k_cache"), py::arg("v_cache"),
           py::arg("cu_q"), py::arg("q_start"), py::arg("block_table"), py::arg("tiles"), py::arg("heads"),
-          py::arg("kv_heads"), py::arg("head_dim"), py::arg("window"), py::arg("scale"), py::arg("status") = py::none());
+          py::arg("kv_heads"), py::arg("head_dim"), py::arg("window"), py::arg("scale"), py::arg("status") = py::none(),
+          py::arg("chunk") = 0);
     m.def("attention_decode", &attention_decode, py::arg("qkv"), py::arg("out"), py::arg("k_cache"), py::arg("v_cache"),
           py::arg("cu_q"), py::arg("q_start"), py::arg("block_table"), py::arg("heads"), py::arg("kv_heads"),
           py::arg("head_dim"), py::arg("window"), py::arg("scale"), py::arg("n_splits"), py::arg("part_o") = py::none(),
           py::arg("part_ml") = py::none(), py::arg("counters") = py::none(), py::arg("fuse_rope") = false,
           py::arg("cos_sin") = py::none(), py::arg("store_kv") = false, py::arg("status") = py::none(),
-          py::arg("qkv_shares") = py::none(), py::arg("long_runs") = false, py::arg("run_blocks") = 0);
+          py::arg("qkv_shares") = py::none(), py::arg("long_runs") = false, py::arg("run_blocks") = 0,
+          py::arg("chunk") = 0);
     m.def("argmax", &argmax, py::arg("logits"), py::arg("out"));
     m.def("sample", &sample, py::arg("logits"), py::arg("temperature"), py::arg("top_k"), py::arg("top_p"),
           py::arg("u"), py::arg("out"));

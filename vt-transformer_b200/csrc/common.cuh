@@ -41,6 +41,15 @@ template <typename T> __device__ __forceinline__ T from_float(float v);
 template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
 template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
+// The first key that a token at position `pos` sees: key 0; with a window, the first of the last `window` keys; with
+// chunks, the first of its own chunk of `chunk` positions (chunks are counted from position 0 of the sequence); the
+// later of the two where both are given.  It never falls as the position grows.
+__device__ __forceinline__ int first_visible_key(int pos, int window, int chunk) {
+    int lo = (window > 0) ? max(0, pos - window + 1) : 0;
+    if (chunk > 0) lo = max(lo, pos / chunk * chunk);
+    return lo;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -250,6 +250,30 @@ cudaError_t launch_polynorm(int dtype, const void* z, const float* coef, float e
     return launch(polynorm_kernel<float>, n_tokens, threads, 0, stream, (const float*)z, coef, eps, (float*)out, inter);
 }
 
+// ------------------------------------------------------------------------- scaled copy into a range of columns
+
+template <typename T>
+__global__ void scale_into_kernel(const T* __restrict__ src, T* __restrict__ dst, long long total, int n, int dst_stride, int dst_col,
+                                  float scale) {
+    pdl_launch();
+    pdl_wait();
+    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (long long)gridDim.x * blockDim.x) {
+        const long long t = e / n;
+        const int i = (int)(e % n);
+        dst[t * dst_stride + dst_col + i] = from_float<T>(to_float(src[e]) * scale);
+    }
+}
+
+cudaError_t launch_scale_into(int dtype, const void* src, void* dst, int n_tokens, int n, int dst_stride, int dst_col, float scale,
+                              cudaStream_t stream) {
+    const long long total = (long long)n_tokens * n;
+    if (total == 0) return cudaSuccess;
+    const int blocks = (int)min((total + 255) / 256, (long long)148 * 16);
+    if (dtype == kBF16)
+        return launch(scale_into_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (const __nv_bfloat16*)src, (__nv_bfloat16*)dst, total, n, dst_stride, dst_col, scale);
+    return launch(scale_into_kernel<float>, blocks, 256, 0, stream, (const float*)src, (float*)dst, total, n, dst_stride, dst_col, scale);
+}
+
 // ------------------------------------------------------------------------- silu * up
 
 template <typename T>

@@ -70,6 +70,10 @@ cudaError_t launch_attention_general(int dtype, const void* y, int stride, int q
                                      int n_tokens, int heads, int kv_heads, int dim, int v_dim, int page_size, int window,
                                      int chunk, float scale, int* status, cudaStream_t stream);
 
+// dst[t, dst_col + i] = scale * src[t, i] for src [n_tokens, n] and dst [n_tokens, dst_stride], the product in 32-bit.
+cudaError_t launch_scale_into(int dtype, const void* src, void* dst, int n_tokens, int n, int dst_stride, int dst_col, float scale,
+                              cudaStream_t stream);
+
 // out[t, i] = silu(gate) * up.  interleave 0: gate = gu[t, i], up = gu[t, inter + i].  interleave 8: gate and up
 // columns alternate in runs of 8 (g0..g7, u0..u7, g8.., ...): gate = gu[t, 16 (i / 8) + i % 8], up 8 further.
 // inter % 8 == 0.
@@ -131,6 +135,8 @@ cudaError_t launch_gemm_tc_pair(const void* x, const void* w, const float* bias,
                                 int bn, float* scratch, long long scratch_floats, int* counters, int n_counters, int* status,
                                 cudaStream_t stream);
 
+// In the three tensor-core attention launchers `chunk` > 0 adds the mask of chunks to the causal mask and the window: a
+// token at position p sees key j only if j / chunk == p / chunk (chunks are counted from position 0 of the sequence).
 // Tensor-core attention over the paged cache (bfloat16).  A tile is 16 * warps rows, row r being
 // (token r / group, head r % group); `tiles` lists (sequence, first token) pairs, or is null when
 // every sequence is one tile (single-token steps).  warps is 1 or 4.  With n_splits > 1 the keys of a
@@ -141,7 +147,7 @@ cudaError_t launch_attention_mma(const void* qkv, int qkv_stride, void* out, con
                                  const int* cu_q, const int* q_start, const int* block_table, int table_stride,
                                  const int* tiles, int n_tiles, int n_pages, int n_tokens, int heads, int kv_heads,
                                  int head_dim, int page_size, int window, float scale, int warps, int n_splits,
-                                 float* part_o, float* part_ml, int* status, cudaStream_t stream);
+                                 float* part_o, float* part_ml, int* status, cudaStream_t stream, int chunk = 0);
 
 // Attention of prompt portions on tcgen05 tensor cores with the scores in tensor memory (head size 128):
 // tiles of 128 rows of (token, head of the group) as in launch_attention_mma with 8 warps.
@@ -149,7 +155,7 @@ bool attention_tc_supports(int head_dim, int heads, int kv_heads);
 cudaError_t launch_attention_tc(const void* qkv, int qkv_stride, void* out, const void* k_cache, const void* v_cache,
                                 const int* cu_q, const int* q_start, const int* block_table, int table_stride,
                                 const int* tiles, int n_tiles, int n_pages, int heads, int kv_heads, int head_dim,
-                                int page_size, int window, float scale, int* status, cudaStream_t stream);
+                                int page_size, int window, float scale, int* status, cudaStream_t stream, int chunk = 0);
 
 // Attention of single-token steps: every sequence brings tokens_per_tile = 16 / group tokens at most (one in a
 // decode step).  Grid (sequences, kv_heads, n_splits), four warps a CTA.  With n_splits > 1 the runs' results
@@ -168,7 +174,7 @@ cudaError_t launch_attention_decode(const void* qkv, int qkv_stride, void* out, 
                                     int page_size, int window, float scale, int n_splits, float* part_o, float* part_ml,
                                     int* counters, int fuse_rope, const float2* cos_sin, int max_pos, int store_kv,
                                     const float* qkv_shares, int n_shares, int long_runs, int run_blocks, int* status,
-                                    cudaStream_t stream);
+                                    cudaStream_t stream, int chunk = 0);
 
 // out[r] = index of the largest logit of row r (the lowest index among equals).
 cudaError_t launch_argmax(const float* logits, int* out, int n_rows, int vocab, cudaStream_t stream);

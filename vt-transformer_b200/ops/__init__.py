@@ -175,6 +175,20 @@ def attention_general(y, q_col: int, out, out_col: int, out_scale: float, k_cach
     return out
 
 
+def scale_into(src: torch.Tensor, dst: torch.Tensor, dst_col: int, scale: float) -> torch.Tensor:
+    """dst[:, dst_col : dst_col + n] = scale * src for src [T, n] (the product in 32-bit, one rounding)."""
+    backend().scale_into(src, dst, int(dst_col), float(scale))
+    return dst
+
+
+def tensor_core_attention_takes(dtype, heads: int, kv_heads: int, head_dim: int, v_dim: int, page_size: int) -> bool:
+    """Whether ``paged_attention`` runs bfloat16 tensor-core kernels at these sizes for every kind of step (values as
+    wide as keys, a head size the kernels take, pages of a multiple of 16 tokens)."""
+    return (dtype == torch.bfloat16 and v_dim == head_dim and page_size % 16 == 0 and ATTENTION_KERNEL in ("auto", "mma")
+            and backend().attention_mma_supports(head_dim, heads, kv_heads, 1)
+            and backend().attention_mma_supports(head_dim, heads, kv_heads, 4))
+
+
 def silu_mul(gu: torch.Tensor, out: torch.Tensor, interleave: int = 0) -> torch.Tensor:
     """out = silu(gate) * up.  ``interleave`` 0: gu = [gate | up]; 8: gate and up columns alternate in
     runs of 8 (``interleave_gate_up``)."""
@@ -406,19 +420,21 @@ FUSE_ROPE = True    # False: always the separate rotation kernel (tests compare 
 
 
 def paged_attention(qkv, out, k_cache, v_cache, ctx, block_table, heads: int, kv_heads: int, head_dim: int,
-                    window: Optional[int], scale: float, status=None) -> torch.Tensor:
+                    window: Optional[int], scale: float, status=None, chunk: Optional[int] = None) -> torch.Tensor:
     """Attention of the step's tokens over the paged keys and values of their sequences.
     ``ctx`` is the step's ``StepContext``.  bfloat16 runs on the tensor cores where the kernel
     takes the sizes (head_dim a multiple of 16 up to 128; tcgen05 for prompt portions at 64 and 128): single-token steps with the keys of a
     sequence split over several CTAs, other steps in tiles of 64 or 128 rows of (token, head of
-    the group).  Everything else, and all of float32, runs the plain kernel."""
+    the group).  Everything else, and all of float32, runs the plain kernel.  ``chunk`` c adds the mask of chunks: key
+    j is seen from position p only if j // c == p // c (the tensor-core kernels take it; the plain kernel does not)."""
     global launches
     be = backend()
     w = int(window) if window else 0
+    c = int(chunk) if chunk else 0
     group = heads // kv_heads
     if qkv.dtype == torch.bfloat16 and ATTENTION_KERNEL in ("auto", "mma"):
         if ctx.max_q_len == 1 and be.attention_mma_supports(head_dim, heads, kv_heads, 1):
-            span = ctx.max_kv_len if not w else min(ctx.max_kv_len, w + 31)
+            span = _key_span(ctx.max_kv_len, w, c)
             splits, run, scratch = _decode_plan(ctx.n_seqs * kv_heads, span, qkv.device, getattr(ctx, "min_kv_len", 0))
             part_o = part_ml = counters = None
             if scratch or splits > 8:
@@ -428,7 +444,7 @@ def paged_attention(qkv, out, k_cache, v_cache, ctx, block_table, heads: int, kv
             long_runs = _decode_long_runs(ctx.n_seqs * kv_heads, span, splits, run, head_dim, qkv.device)
             be.attention_decode(qkv, out, k_cache, v_cache, ctx.cu_q, ctx.q_start, block_table, heads, kv_heads,
                                 head_dim, w, float(scale), splits, part_o, part_ml, counters, long_runs=long_runs,
-                                run_blocks=run)
+                                run_blocks=run, chunk=c)
             return out
         # portions long enough to fill tiles of 128 rows: the tcgen05 kernel where it takes the sizes
         if (ATTENTION_KERNEL == "auto" and ctx.max_q_len * group >= 128
@@ -439,7 +455,7 @@ def paged_attention(qkv, out, k_cache, v_cache, ctx, block_table, heads: int, kv
             lead = _leading_single_tokens(ctx)
             if lead >= MIXED_STEP_MIN_SINGLES and be.attention_mma_supports(head_dim, heads, kv_heads, 1):
                 longest = max(s.start + 1 for s in ctx.seqs[:lead])
-                span = longest if not w else min(longest, w + 31)
+                span = _key_span(longest, w, c)
                 splits, run, scratch = _decode_plan(lead * kv_heads, span, qkv.device)
                 part_o = part_ml = counters = None
                 if scratch or splits > 8:
@@ -450,23 +466,31 @@ def paged_attention(qkv, out, k_cache, v_cache, ctx, block_table, heads: int, kv
                 launches += 1
                 be.attention_decode(qkv[:lead], out[:lead], k_cache, v_cache, ctx.cu_q[:lead + 1], ctx.q_start[:lead],
                                     block_table[:lead], heads, kv_heads, head_dim, w, float(scale), splits, part_o, part_ml,
-                                    counters, long_runs=long_runs, run_blocks=run)
+                                    counters, long_runs=long_runs, run_blocks=run, chunk=c)
             else:
                 lead = 0
             tiles = _attention_tiles(ctx, 128 // group, qkv.device, first_seq=lead)
             be.attention_tc(qkv, out, k_cache, v_cache, ctx.cu_q, ctx.q_start, block_table, tiles, heads, kv_heads,
-                            head_dim, w, float(scale), status)
+                            head_dim, w, float(scale), status, chunk=c)
             return out
         # mma.sync tiles of 128 rows (8 warps) where the portions are long enough to fill them, else of 64
         warps = 8 if ctx.max_q_len * group >= 128 and be.attention_mma_supports(head_dim, heads, kv_heads, 8) else 4
         if be.attention_mma_supports(head_dim, heads, kv_heads, warps):
             tiles = _attention_tiles(ctx, (16 * warps) // group, qkv.device)
             be.attention_mma(qkv, out, k_cache, v_cache, ctx.cu_q, ctx.q_start, block_table, tiles, heads, kv_heads,
-                             head_dim, w, float(scale), warps, 1, None, None, status)
+                             head_dim, w, float(scale), warps, 1, None, None, status, chunk=c)
             return out
+    if c:
+        raise ValueError("paged_attention: the plain kernel has no mask of chunks; ops.attention_general has")
     be.attention_simt(qkv, out, k_cache, v_cache, ctx.positions, ctx.token_seq, block_table, heads, kv_heads,
                       head_dim, w, float(scale), status)
     return out
+
+
+def _key_span(longest: int, window: int, chunk: int) -> int:
+    """The most keys a token of a step can see, for the plan of a single-token step's CTAs."""
+    span = longest if not window else min(longest, window + 31)
+    return min(span, chunk) if chunk else span
 
 
 _sm_counts = {}
@@ -586,6 +610,6 @@ def _counted(fn):
     return wrapper
 
 
-for _name in ("embedding", "logits_scale_cap", "rmsnorm", "layernorm", "polynorm", "head_norm_gate", "gla_scan", "delta_scan",
+for _name in ("embedding", "logits_scale_cap", "rmsnorm", "layernorm", "polynorm", "scale_into", "head_norm_gate", "gla_scan", "delta_scan",
               "attention_prepare", "attention_general", "silu_mul", "rope_store", "linear", "paged_attention", "argmax", "sample"):  # the others count where they launch
     globals()[_name] = _counted(globals()[_name])

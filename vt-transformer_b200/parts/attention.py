@@ -163,5 +163,17 @@ class GeneralAttention(ProjectedMixer):
         k_pages, v_pages = cache.pages["k"], cache.pages["v"]
         ops.attention_prepare(y, cols[0], cols[1], cols[2], ctx, freq, s.qk_norm_eps, k_pages, v_pages, cache.block_table,
                               s.heads, s.kv_heads, s.head_dim, self.v_dim, store=cache.writes, status=ctx.status)
+        if cols[0] == 0 and ops.tensor_core_attention_takes(y.dtype, s.heads, s.kv_heads, s.head_dim, self.v_dim, cache.page_size):
+            # values as wide as keys at a head size the tensor-core kernels take: the kernels of the plain attention walk
+            # the keys (tcgen05 for long portions, mma.sync tiles, the single-token kernel), with the chunks as one more
+            # bound of the keys a row sees.  They write a tensor of their own, which is then scaled into its columns.
+            n = s.heads * self.v_dim
+            direct = out_col == 0 and out.shape[1] == n and out_scale == 1.0
+            o = out if direct else torch.empty((y.shape[0], n), dtype=y.dtype, device=y.device)
+            ops.paged_attention(y, o, k_pages, v_pages, ctx, cache.block_table, s.heads, s.kv_heads, s.head_dim, s.window,
+                                self.scale, status=ctx.status, chunk=s.chunk)
+            if not direct:
+                ops.scale_into(o, out, out_col, out_scale)
+            return
         ops.attention_general(y, cols[0], out, out_col, out_scale, k_pages, v_pages, ctx, cache.block_table, s.heads,
                               s.kv_heads, s.head_dim, self.v_dim, s.window, s.chunk, self.scale, status=ctx.status)
