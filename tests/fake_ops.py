@@ -154,10 +154,11 @@ def layernorm(x, delta, weight, eps, out, rows=None, status=None):
     out.copy_((weight * dev * torch.rsqrt((dev * dev).mean(dim=-1, keepdim=True) + eps)).to(out.dtype))
 
 
-def polynorm(z, coefficients, eps, out):
+def polynorm(z, coefficients, eps, out, n_mean=0):
     a, b, c, e = [float(v) for v in coefficients]
     zf = z.float()
-    n = lambda y: y * torch.rsqrt((y * y).mean(dim=-1, keepdim=True) + eps)
+    count = n_mean if n_mean > 0 else z.shape[1]
+    n = lambda y: y * torch.rsqrt((y * y).sum(dim=-1, keepdim=True) / count + eps)
     out.copy_((a * n(zf) + b * n(zf * zf) + c * n(zf * zf * zf) + e).to(out.dtype))
 
 

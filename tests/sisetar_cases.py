@@ -41,7 +41,7 @@ def _model(vocab, width, layers, emb=1.0, logit_scale=1.0, cap=0.0, eps=1e-5):
 # own of the scan kernel), sizes that are no multiples of 8, 16 or 32.
 CONFIGS: Dict[str, dict] = {
     "mix": _model(300, 64, [_par(4, 4, 32, 48, 32, 100.0, 0.3, 7, 2, 40, 1.0, 1.0, ff=96), _gla(3, 24, 40, 4.0, ff=72),
-                            _gla(1, 32, 32, 1.0), _par(4, 1, 40, 16, 8, 5000.0, 0.11, 33, 1, 16, 0.5, 2.0)],
+                            _gla(1, 32, 32, 1.0), _par(4, 1, 40, 16, 8, 5000.0, 0.11, 33, 1, 16, 0.5, 2.0, ff=50)],
                   emb=3.0, logit_scale=0.7, cap=8.0),
     "wide": _model(257, 72, [_gla(2, 136, 72, 8.0), _par(2, 1, 72, 20, 0, 10000.0, 0.2, 50, 1, 160, 1.5, 0.6, ff=40),
                              _gla(1, 72, 100, 2.0)], emb=1.0, logit_scale=1.0, cap=0.0, eps=1e-6),

@@ -28,7 +28,7 @@ def test_configuration_reads_every_size_and_round_trips():
     assert isinstance(cfg, SisetarConfig) and cfg.vocab == 300 and cfg.width == 64 and len(cfg.layers) == 4
     left = cfg.layers[3].mixer.left
     assert (left.heads, left.kv_heads, left.dim, left.vdim, left.rot_dims, left.chunk) == (4, 1, 40, 16, 8, 33)
-    assert cfg.layers[1].ff == 72 and cfg.layers[2].ff is None and cfg.layers[1].mixer.tau == 4.0
+    assert cfg.layers[1].ff == 72 and cfg.layers[2].ff is None and cfg.layers[3].ff == 50 and cfg.layers[1].mixer.tau == 4.0
     assert config_from_dict(cfg.to_dict()) == cfg
     bad = copy.deepcopy(cases.CONFIGS["mix"])
     bad["layers"][0]["type"] = "other"
@@ -55,7 +55,7 @@ def test_the_model_declares_pages_and_states_for_what_its_layers_keep():
     assert slots[0] == KVCacheSpec(4, 32, None, v_dim=48) and slots[1].shape == (2, 40, 40) and slots[2].shape == (3, 24, 40)
     names = set(model.param_specs())
     assert {"embed", "final.norm", "l0.norm2", "l0.mix.left.q", "l0.mix.right.w0", "l1.mix.a2.b", "l1.mlp.act"} <= names
-    assert "l2.norm2" not in names and "l3.mlp.up" not in names and "l2.mlp.act" not in names
+    assert "l2.norm2" not in names and "l2.mlp.up" not in names and "l2.mlp.act" not in names
     assert model.graph_safe()
 
 

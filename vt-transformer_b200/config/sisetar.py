@@ -98,8 +98,6 @@ class SisetarConfig(ModelConfig):
             raise ConfigError(f"{where}: 'logit_softcap' must not be negative")
         for i, layer in enumerate(self.layers):
             at = f"{where}: layers[{i}]"
-            if layer.ff is not None and layer.ff % 8:
-                raise ConfigError(f"{at}: mlp 'ff' {layer.ff} must be a multiple of 8")
             att = layer.mixer.left if layer.type == "parallel" else None
             if att is not None:
                 if att.heads % att.kv_heads:

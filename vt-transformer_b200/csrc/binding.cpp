@@ -114,14 +114,16 @@ void layernorm(Tensor& x, c10::optional<Tensor> delta, const Tensor& weight, dou
     norm_rows(true, x, delta, weight, eps, out, rows, status);
 }
 
-void polynorm(const Tensor& z, const Tensor& coef, double eps, Tensor& out) {
+void polynorm(const Tensor& z, const Tensor& coef, double eps, Tensor& out, int64_t n_mean) {
     check_cuda(z, "z"); check_cuda(out, "out"); check_f32(coef, "coefficients");
     TORCH_CHECK(z.dim() == 2 && out.sizes() == z.sizes() && out.scalar_type() == z.scalar_type(), "polynorm: out must be like z [tokens, inter]");
     TORCH_CHECK(coef.numel() == 4, "polynorm: four coefficients");
     TORCH_CHECK(z.size(1) % 8 == 0, "polynorm: inner size ", z.size(1), " must be a multiple of 8");
+    if (n_mean <= 0) n_mean = z.size(1);
+    TORCH_CHECK(n_mean <= z.size(1), "polynorm: more columns to average than the row has");
     c10::cuda::CUDAGuard guard(z.device());
     check_launch(vtb::launch_polynorm(dtype_code(z, "z"), z.data_ptr(), coef.data_ptr<float>(), (float)eps, out.data_ptr(), z.size(0),
-                                      z.size(1), stream_of(z)), "polynorm");
+                                      z.size(1), n_mean, stream_of(z)), "polynorm");
 }
 
 // columns [col, col + n) of a row-major [tokens, stride] tensor
@@ -657,7 +659,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("rows") = py::none(), py::arg("status") = py::none());
     m.def("layernorm", &layernorm, py::arg("x"), py::arg("delta"), py::arg("weight"), py::arg("eps"), py::arg("out"),
           py::arg("rows") = py::none(), py::arg("status") = py::none());
-    m.def("polynorm", &polynorm);
+    m.def("polynorm", &polynorm, py::arg("z"), py::arg("coefficients"), py::arg("eps"), py::arg("out"), py::arg("n_mean") = 0);
     m.def("scale_into", &scale_into);
     m.def("head_norm_gate", &head_norm_gate, py::arg("o"), py::arg("y"), py::arg("gate_col"), py::arg("weight"),
           py::arg("weight_per_channel"), py::arg("eps"), py::arg("act"), py::arg("out"), py::arg("out_col"), py::arg("out_scale"),

@@ -202,10 +202,10 @@ cudaError_t launch_layernorm(int out_dtype, float* x, const void* delta, const f
 // ------------------------------------------------------------------------- PolyNorm
 
 // One block a row: out = a N(z) + b N(z^2) + c N(z^3) + e with N(y) = y / sqrt(mean(y^2) + eps).  Pass 1 sums z^2,
-// z^4 and z^6 in 32-bit; pass 2 reads the row again (each thread the values it read before, so `out` may be `z`).
+// z^4 and z^6 in 32-bit (the means are over the first n_mean columns; the others are zero padding); pass 2 reads the row again (each thread the values it read before, so `out` may be `z`).
 template <typename T>
 __global__ void polynorm_kernel(const T* __restrict__ z, const float* __restrict__ coef, float eps, T* __restrict__ out,
-                                int inter) {
+                                int inter, int n_mean) {
     __shared__ float scratch[32];
     pdl_launch();
     const float a = coef[0], b = coef[1], c = coef[2], e = coef[3];      // weights: written by no kernel of the step
@@ -224,7 +224,7 @@ __global__ void polynorm_kernel(const T* __restrict__ z, const float* __restrict
             s6 = fmaf(p2 * p2, p2, s6);
         }
     }
-    const float n = (float)inter;
+    const float n = (float)n_mean;     // columns beyond n_mean are padding (zeros): they add nothing to the sums
     const float r1 = a * rsqrtf(block_sum(s2, scratch) / n + eps);
     const float r2 = b * rsqrtf(block_sum(s4, scratch) / n + eps);
     const float r3 = c * rsqrtf(block_sum(s6, scratch) / n + eps);
@@ -241,13 +241,13 @@ __global__ void polynorm_kernel(const T* __restrict__ z, const float* __restrict
 }
 
 cudaError_t launch_polynorm(int dtype, const void* z, const float* coef, float eps, void* out, int n_tokens, int inter,
-                            cudaStream_t stream) {
+                            int n_mean, cudaStream_t stream) {
     if (n_tokens == 0) return cudaSuccess;
     if (inter % 8) return cudaErrorInvalidValue;
     const int threads = min(512, max(32, ((inter / 8 + 31) / 32) * 32));
     if (dtype == kBF16)
-        return launch(polynorm_kernel<__nv_bfloat16>, n_tokens, threads, 0, stream, (const __nv_bfloat16*)z, coef, eps, (__nv_bfloat16*)out, inter);
-    return launch(polynorm_kernel<float>, n_tokens, threads, 0, stream, (const float*)z, coef, eps, (float*)out, inter);
+        return launch(polynorm_kernel<__nv_bfloat16>, n_tokens, threads, 0, stream, (const __nv_bfloat16*)z, coef, eps, (__nv_bfloat16*)out, inter, n_mean);
+    return launch(polynorm_kernel<float>, n_tokens, threads, 0, stream, (const float*)z, coef, eps, (float*)out, inter, n_mean);
 }
 
 // ------------------------------------------------------------------------- scaled copy into a range of columns

@@ -29,9 +29,10 @@ cudaError_t launch_layernorm(int out_dtype, float* x, const void* delta, const f
                              int hidden, int* status, cudaStream_t stream);
 
 // out[t, :] = a N(z) + b N(z^2) + c N(z^3) + e for every row of z [n_tokens, inter], N(y) = y / sqrt(mean(y^2) + eps),
-// (a, b, c, e) = coef[0..3].  out may be z.  inter % 8 == 0.
+// (a, b, c, e) = coef[0..3].  out may be z.  inter % 8 == 0; the means are over the first n_mean columns, the rest being
+// zero padding.
 cudaError_t launch_polynorm(int dtype, const void* z, const float* coef, float eps, void* out, int n_tokens, int inter,
-                            cudaStream_t stream);
+                            int n_mean, cudaStream_t stream);
 
 // Gated linear attention over the tokens of every (sequence, head) in order (recurrent.cu).  y [tokens, stride] holds
 // q, k [heads * dim], v [heads * v_dim] and the low-rank gate's input [rank] at the given columns; a2 [heads * dim,

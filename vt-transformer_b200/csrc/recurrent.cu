@@ -21,6 +21,7 @@ namespace {
 constexpr int kScanCols = 32;     // columns of the state a warp owns
 constexpr int kScanThreads = 256; // most threads of a CTA
 constexpr int kScanTokens = 16;   // tokens staged in shared memory at once
+constexpr int kScanValues = 8;    // values of a token that a thread fetches through its fixed shares
 
 struct ScanArgs {
     const void* y;                // [tokens, stride]: the projections
@@ -52,8 +53,9 @@ __device__ __forceinline__ float sigmoid(float z) { return 1.f / (1.f + expf(-z)
 
 // A CTA owns `col_blocks` * 32 columns of one (sequence, head): thread (c, g, cb) keeps rows [g KD, (g + 1) KD) of column
 // (blockIdx.z col_blocks + cb) 32 + c in registers.  The step's tokens of the sequence are staged in batches of 16: all
-// threads fetch the batch's projections (independent loads, many in flight), form decay, removal rate and unit key
-// from them once for all columns, and then walk the batch's tokens out of shared memory.
+// threads fetch the batch's projections (each thread the same columns of every token, four tokens' loads in flight at
+// once), form decay, removal rate and unit key from them once for all columns, and then walk the batch's tokens out of
+// shared memory.
 template <typename T, int KD, bool Delta>
 __global__ void __launch_bounds__(kScanThreads, 1)
 scan_kernel(const ScanArgs a) {
@@ -120,6 +122,35 @@ scan_kernel(const ScanArgs a) {
         vs[tb * cols + r - rank] = v;
     };
 
+    // Which of a token's values this thread fetches is the same for every token: value r = tid + k * threads comes from
+    // column from_col[k] of the token's row (-1: padding, nothing to load), is multiplied by times[k] and lands at
+    // smem[to_at[k] + token * to_step[k]] (-1: no such value).
+    int from_col[kScanValues], to_at[kScanValues], to_step[kScanValues];
+    float times[kScanValues];
+    bool is_low[kScanValues];
+#pragma unroll
+    for (int k = 0; k < kScanValues; ++k) {
+        int r = tid + k * n_threads;
+        from_col[k] = -1; to_at[k] = -1; to_step[k] = 0; times[k] = 1.f; is_low[k] = false;
+        if (r >= per) continue;
+        if (r < kVectors * dim_p) {
+            const int which = r < dim_p ? 0 : (r < 2 * dim_p ? 1 : 2), i = r - which * dim_p;
+            to_at[k] = (int)((which == 0 ? qs : (which == 1 ? ks : bs)) - smem) + i;
+            to_step[k] = dim_p;
+            if (i < dim) from_col[k] = (which == 0 ? a.q_col : (which == 1 ? a.k_col : a.a_col)) + h * dim + i;
+            if (!Delta && which == 0) times[k] = a.c2;
+            continue;
+        }
+        r -= kVectors * dim_p;
+        if (r < rank) {
+            to_at[k] = (int)(low - smem) + r; to_step[k] = rank; from_col[k] = a.low_col + r; is_low[k] = true;
+            continue;
+        }
+        r -= rank;
+        to_at[k] = (int)(vs - smem) + r; to_step[k] = cols;
+        if (col0 + r < v_dim) from_col[k] = a.v_col + h * v_dim + col0 + r;
+    }
+
     float* sp = a.state + (((size_t)row * a.heads + h) * dim) * v_dim;
     float S[KD];
 #pragma unroll
@@ -131,10 +162,30 @@ scan_kernel(const ScanArgs a) {
     for (int tb0 = t0; tb0 < t1; tb0 += TB) {
         const int n = min(TB, t1 - tb0);
         __syncthreads();                                    // the batch before is done with
-#pragma unroll 4
-        for (int tb = 0; tb < n; ++tb) {
+        // four tokens' values at a time: up to 32 loads a thread that wait for nothing but memory
+        for (int tb = 0; tb < n; tb += 4) {
+            float val[4][kScanValues];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const T* yr = y + (size_t)(tb0 + min(tb + u, n - 1)) * a.stride;
+#pragma unroll
+                for (int k = 0; k < kScanValues; ++k) val[u][k] = from_col[k] >= 0 ? to_float(yr[from_col[k]]) : 0.f;
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (tb + u >= n) break;
+#pragma unroll
+                for (int k = 0; k < kScanValues; ++k) {
+                    if (to_at[k] < 0) continue;
+                    float v = val[u][k] * times[k];
+                    if (Delta && is_low[k]) v = tanhf(v);
+                    smem[to_at[k] + (tb + u) * to_step[k]] = v;
+                }
+            }
+        }
+        for (int tb = 0; tb < n; ++tb) {                    // sizes beyond what the threads' fixed shares cover
             const T* yr = y + (size_t)(tb0 + tb) * a.stride;
-            for (int r = tid; r < per; r += n_threads) place(tb, r, fetch(yr, r));
+            for (int r = tid + kScanValues * n_threads; r < per; r += n_threads) place(tb, r, fetch(yr, r));
         }
         __syncthreads();
         for (int e = tid; e < n * dim_p; e += n_threads) {

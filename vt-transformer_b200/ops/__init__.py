@@ -105,10 +105,11 @@ def layernorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tens
     return out
 
 
-def polynorm(z: torch.Tensor, coefficients: torch.Tensor, eps: float, out: torch.Tensor) -> torch.Tensor:
+def polynorm(z: torch.Tensor, coefficients: torch.Tensor, eps: float, out: torch.Tensor, n_mean: int = 0) -> torch.Tensor:
     """out = a N(z) + b N(z^2) + c N(z^3) + e row by row, N(y) = y / sqrt(mean(y^2) + eps), (a, b, c, e) the four
-    float32 numbers of ``coefficients``; powers and means in 32-bit.  ``out`` may be ``z``."""
-    backend().polynorm(z, coefficients, float(eps), out)
+    float32 numbers of ``coefficients``; powers and means in 32-bit.  ``out`` may be ``z``.  With ``n_mean`` the means
+    are over the first n_mean columns (the others are zero padding of a product whose matrix was padded)."""
+    backend().polynorm(z, coefficients, float(eps), out, int(n_mean))
     return out
 
 

@@ -72,8 +72,11 @@ class PolyNormMLP(FeedForward):
     def load(self, get) -> None:
         s, p, rt = self.spec, self.prefix, self.rt
         u, d, act = s.names
-        self.w_up = rt.param(get(f"{p}{u}"))
-        self.w_down = rt.param(get(f"{p}{d}"))
+        # an inner size that is no multiple of 8 is padded to one (rows of zeros in up, columns of zeros in down): the
+        # products read rows in 16-byte pieces; the activation's means are over the real columns
+        from .projected import pack_columns, pack_rows
+        self.w_up, _ = pack_rows([rt.param(get(f"{p}{u}"))])
+        self.w_down, _, _ = pack_columns([rt.param(get(f"{p}{d}"))])
         self.coefficients = rt.param(get(f"{p}{act}"), "vector")
 
     def weight_bytes(self) -> int:
@@ -84,7 +87,7 @@ class PolyNormMLP(FeedForward):
 
     def forward(self, h, ctx):
         s, ops = self.spec, self.rt.ops
-        z = torch.empty((h.shape[0], s.inter), dtype=h.dtype, device=h.device)
+        z = torch.empty((h.shape[0], self.w_up.shape[0]), dtype=h.dtype, device=h.device)
         ops.linear(h, self.w_up, None, z, then=ops.product_hint(self.w_down, "stream"))
-        ops.polynorm(z, self.coefficients, s.eps, z)
+        ops.polynorm(z, self.coefficients, s.eps, z, n_mean=s.inter)
         return ops.linear_to_stream(z, self.w_down, None, then=self.then)
