@@ -4,10 +4,10 @@
 // The recurrences, for one head with state S [dim, v_dim] in 32-bit:
 //   gated linear attention   S <- diag(alpha_t) S + k_t v_t^T,                         o_t = S^T q_t
 //   delta rule               S <- diag(w_t) S - (a_t * u_t)(u_t^T S_old) + k_t v_t^T,  o_t = S^T r_t
-// Column j of S depends on column j alone, so a CTA owns 32 columns of one (sequence, head) and walks the step's
+// Column j of S depends on column j alone, so a warp owns 32 columns of one (sequence, head) and walks the step's
 // tokens of that sequence in order: a decoded token and a portion of a prompt are the same loop.  A thread keeps
-// KD rows of its column in registers; with dim > KD the rows are spread over `G` threads a column, whose partial dot
-// products meet in shared memory in the order of g.  What enters the recurrence is formed in 32-bit while a batch of
+// KD rows of its column in registers; the rows are spread over `G` threads a column (G warps), whose partial dot
+// products meet in shared memory and are added in the order of g.  What enters the recurrence is formed in 32-bit while a batch of
 // tokens is staged in shared memory: the decay from its low-rank gate (log-sigmoid and exp, or sigmoid and exp), the
 // removal rate, the unit key.  The sums' order depends on dim alone, never on how the tokens were cut into steps.
 #include "common.cuh"
@@ -19,9 +19,11 @@ namespace vtb {
 namespace {
 
 constexpr int kScanCols = 32;     // columns of the state a warp owns
-constexpr int kScanThreads = 256; // most threads of a CTA
+// most threads of a CTA, by the rows a thread keeps in registers
+constexpr int scan_threads(int kd) { return kd <= 32 ? 1024 : (kd <= 64 ? 512 : 256); }
 constexpr int kScanTokens = 16;   // tokens staged in shared memory at once
-constexpr int kScanValues = 8;    // values of a token that a thread fetches through its fixed shares
+// values of a token that a thread fetches through its fixed shares (the more threads a CTA has, the fewer each needs)
+constexpr int scan_values(int kd) { return kd <= 32 ? 2 : (kd <= 64 ? 4 : 8); }
 
 struct ScanArgs {
     const void* y;                // [tokens, stride]: the projections
@@ -57,7 +59,7 @@ __device__ __forceinline__ float sigmoid(float z) { return 1.f / (1.f + expf(-z)
 // once), form decay, removal rate and unit key from them once for all columns, and then walk the batch's tokens out of
 // shared memory.
 template <typename T, int KD, bool Delta>
-__global__ void __launch_bounds__(kScanThreads, 1)
+__global__ void __launch_bounds__(scan_threads(KD), 1)
 scan_kernel(const ScanArgs a) {
     extern __shared__ __align__(16) float smem[];
     pdl_launch();
@@ -65,6 +67,7 @@ scan_kernel(const ScanArgs a) {
     const int c = threadIdx.x, g = threadIdx.y, cb = threadIdx.z;
     const int G = a.groups, CB = a.col_blocks;
     constexpr int TB = kScanTokens;
+    constexpr int kScanValues = scan_values(KD);
     const int tid = (cb * G + g) * kScanCols + c, n_threads = kScanCols * G * CB;
     const int dim = a.dim, v_dim = a.v_dim, rank = a.rank;
     const int dim_p = G * KD, cols = CB * kScanCols;
@@ -82,7 +85,8 @@ scan_kernel(const ScanArgs a) {
     float* ds = bs + (Delta ? TB * dim_p : 0);              // the decay
     float* us = ds + TB * dim_p;                            // delta rule: the unit key
     float* vs = us + (Delta ? TB * dim_p : 0);              // [tokens, cols]
-    float* red = vs + TB * cols;                            // [2, CB, G, 32]
+    float* red = vs + TB * cols;                            // [2, CB, G, 32]: where the groups of a column meet inside a token
+    float* op = red + 2 * CB * G * kScanCols;               // [tokens, G, cols]: the groups' shares of the outputs
     // the weights are written by no kernel of the step: they are read before the wait
     for (int e = tid; e < dim * rank; e += n_threads) w2s[e] = a.w2[(size_t)h * dim * rank + e];
     pdl_wait();
@@ -162,17 +166,19 @@ scan_kernel(const ScanArgs a) {
     for (int tb0 = t0; tb0 < t1; tb0 += TB) {
         const int n = min(TB, t1 - tb0);
         __syncthreads();                                    // the batch before is done with
-        // four tokens' values at a time: up to 32 loads a thread that wait for nothing but memory
-        for (int tb = 0; tb < n; tb += 4) {
-            float val[4][kScanValues];
+        // four tokens' values at a time: loads that wait for nothing but memory (the whole batch at once was measured and
+        // was no faster: a prompt's portion 5 % slower, a decode step's scan 35 %)
+        constexpr int kAtOnce = 4;
+        for (int tb = 0; tb < n; tb += kAtOnce) {
+            float val[kAtOnce][kScanValues];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
+            for (int u = 0; u < kAtOnce; ++u) {
                 const T* yr = y + (size_t)(tb0 + min(tb + u, n - 1)) * a.stride;
 #pragma unroll
                 for (int k = 0; k < kScanValues; ++k) val[u][k] = from_col[k] >= 0 ? to_float(yr[from_col[k]]) : 0.f;
             }
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
+            for (int u = 0; u < kAtOnce; ++u) {
                 if (tb + u >= n) break;
 #pragma unroll
                 for (int k = 0; k < kScanValues; ++k) {
@@ -242,9 +248,11 @@ scan_kernel(const ScanArgs a) {
                 }
                 float us_old = (part[0] + part[1]) + (part[2] + part[3]);
                 if (G > 1) {
+                    // u^T S of the old state is needed before the update: the G warps that share these columns meet
+                    // (a barrier of their own; two buffers in turn, so one meeting a token is enough)
                     float* m = red + ((meet++ & 1) * CB + cb) * G * kScanCols;
                     m[g * kScanCols + c] = us_old;
-                    __syncthreads();
+                    asm volatile("bar.sync %0, %1;" ::"r"(cb + 1), "r"(G * kScanCols) : "memory");
                     us_old = 0.f;
                     for (int gg = 0; gg < G; ++gg) us_old += m[gg * kScanCols + c];
                 }
@@ -274,15 +282,17 @@ scan_kernel(const ScanArgs a) {
                     acc[3] = fmaf(S[4 * i + 3], q.w, acc[3]);
                 }
             }
-            float o = (acc[0] + acc[1]) + (acc[2] + acc[3]);
-            if (G > 1) {
-                float* m = red + ((meet++ & 1) * CB + cb) * G * kScanCols;
-                m[g * kScanCols + c] = o;
-                __syncthreads();
-                o = 0.f;
-                for (int gg = 0; gg < G; ++gg) o += m[gg * kScanCols + c];
-            }
-            if (g == 0 && col_ok) a.out[(size_t)(tb0 + tb) * a.heads * v_dim + h * v_dim + j] = o;
+            // this group's share of the token's output: nothing of the recurrence waits for the sum over the groups,
+            // which is formed once the batch is through
+            op[(tb * G + g) * cols + cb * kScanCols + c] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+        }
+        __syncthreads();
+        for (int e = tid; e < n * cols; e += n_threads) {
+            const int tb = e / cols, cc = e % cols;
+            if (col0 + cc >= v_dim) continue;
+            float o = 0.f;
+            for (int gg = 0; gg < G; ++gg) o += op[(tb * G + gg) * cols + cc];       // in the order of the groups
+            a.out[(size_t)(tb0 + tb) * a.heads * v_dim + h * v_dim + col0 + cc] = o;
         }
     }
 #pragma unroll
@@ -298,12 +308,14 @@ cudaError_t launch_scan_kd(ScanArgs a, int n_seqs, cudaStream_t stream) {
     const int G = a.groups, dim_p = G * KD;
     // as many warps of columns a CTA as the head has, within the CTA's threads
     const int col_warps = (a.v_dim + kScanCols - 1) / kScanCols;
-    const int most = max(1, kScanThreads / (kScanCols * G));
+    // (a group of warps that meets inside a token has a barrier of its own, of which a CTA has 15)
+    const int most = max(1, min(scan_threads(KD) / (kScanCols * G), G > 1 ? 15 : 32));
     const int ctas = (col_warps + most - 1) / most;                       // CTAs a head, with its warps of columns spread evenly
     a.col_blocks = (col_warps + ctas - 1) / ctas;
     const int cols = a.col_blocks * kScanCols;
     const size_t floats = ((a.dim * a.rank + 3) & ~3) + ((kScanTokens * a.rank + 3) & ~3)
-                          + (size_t)(Delta ? 5 : 3) * kScanTokens * dim_p + kScanTokens * cols + 2 * a.col_blocks * G * kScanCols;
+                          + (size_t)(Delta ? 5 : 3) * kScanTokens * dim_p + kScanTokens * cols + 2 * a.col_blocks * G * kScanCols
+                          + (size_t)kScanTokens * G * cols;
     const size_t bytes = floats * sizeof(float);
     constexpr int kMostBytes = 200 * 1024;
     if (bytes > kMostBytes) return cudaErrorInvalidValue;
@@ -316,11 +328,15 @@ cudaError_t launch_scan_kd(ScanArgs a, int n_seqs, cudaStream_t stream) {
 
 template <typename T, bool Delta>
 cudaError_t launch_scan_t(ScanArgs a, int n_seqs, cudaStream_t stream) {
-    // rows a thread: the smallest of 32, 64, 128 that holds dim; beyond 128 the rows are spread over groups of 128
-    if (a.dim <= 32) { a.groups = 1; return launch_scan_kd<T, 32, Delta>(a, n_seqs, stream); }
-    if (a.dim <= 64) { a.groups = 1; return launch_scan_kd<T, 64, Delta>(a, n_seqs, stream); }
-    a.groups = (a.dim + 127) / 128;
+    // Rows a thread: 16 where that makes at most 8 groups of warps a column, else 32, 64, 128.  Few rows a thread make
+    // the walk along the tokens short (a token costs a thread rows / 4 steps of loads and multiply-adds, whatever the
+    // number of groups), which is what bounds a sequence's portion of a prompt; the groups' shares meet in shared memory.
+    const int kd = a.dim <= 128 ? 16 : (a.dim <= 256 ? 32 : (a.dim <= 512 ? 64 : 128));
+    a.groups = (a.dim + kd - 1) / kd;
     if (a.groups > 8) return cudaErrorInvalidValue;
+    if (kd == 16) return launch_scan_kd<T, 16, Delta>(a, n_seqs, stream);
+    if (kd == 32) return launch_scan_kd<T, 32, Delta>(a, n_seqs, stream);
+    if (kd == 64) return launch_scan_kd<T, 64, Delta>(a, n_seqs, stream);
     return launch_scan_kd<T, 128, Delta>(a, n_seqs, stream);
 }
 
