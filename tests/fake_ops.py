@@ -179,7 +179,8 @@ def _sequences(cu_q, rows):
     return [(int(rows[i]), cu[i], cu[i + 1]) for i in range(len(cu) - 1) if cu[i + 1] > cu[i]]
 
 
-def gla_scan(y, q_col, k_col, v_col, a_col, a2, a2_bias, inv_tau, q_scale, state, cu_q, rows, o, heads, dim, v_dim, status=None):
+def gla_scan(y, q_col, k_col, v_col, a_col, a2, a2_bias, inv_tau, q_scale, state, cu_q, rows, o, heads, dim, v_dim, status=None,
+             most_threads=0):
     rank = a2.shape[1]
     yf = y.float()
     z = yf[:, a_col:a_col + rank] @ a2.t() + a2_bias
@@ -196,7 +197,7 @@ def gla_scan(y, q_col, k_col, v_col, a_col, a2, a2_bias, inv_tau, q_scale, state
 
 
 def delta_scan(y, r_col, k_col, v_col, a_col, w1_col, w2, w0, a_bias, decay_rate, key_eps, state, cu_q, rows, o, heads, dim,
-               status=None):
+               status=None, most_threads=0):
     rank = w2.shape[1]
     yf = y.float()
     n = heads * dim

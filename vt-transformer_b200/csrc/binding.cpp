@@ -170,7 +170,7 @@ void check_scan(const Tensor& y, const Tensor& state, const Tensor& cu_q, const 
 
 void gla_scan(const Tensor& y, int64_t q_col, int64_t k_col, int64_t v_col, int64_t low_col, const Tensor& a2, const Tensor& a2_bias,
               double inv_tau, double q_scale, Tensor& state, const Tensor& cu_q, const Tensor& rows, Tensor& o, int64_t heads,
-              int64_t dim, int64_t v_dim, c10::optional<Tensor> status) {
+              int64_t dim, int64_t v_dim, c10::optional<Tensor> status, int64_t most_threads) {
     check_scan(y, state, cu_q, rows, o, heads, dim, v_dim, "gla_scan");
     check_f32(a2, "a2"); check_f32(a2_bias, "a2_bias");
     TORCH_CHECK(a2.dim() == 2 && a2.size(0) == heads * dim && a2_bias.numel() == heads * dim, "gla_scan: a2 [heads * dim, rank] and its bias");
@@ -181,12 +181,12 @@ void gla_scan(const Tensor& y, int64_t q_col, int64_t k_col, int64_t v_col, int6
     check_launch(vtb::launch_gla_scan(dtype_code(y, "y"), y.data_ptr(), y.size(1), q_col, k_col, v_col, low_col, rank, a2.data_ptr<float>(),
                                       a2_bias.data_ptr<float>(), (float)inv_tau, (float)q_scale, state.data_ptr<float>(), state.size(0),
                                       cu_q.data_ptr<int>(), rows.data_ptr<int>(), rows.numel(), o.data_ptr<float>(), heads, dim, v_dim,
-                                      status_ptr(status), stream_of(y)), "gla_scan");
+                                      (int)most_threads, status_ptr(status), stream_of(y)), "gla_scan");
 }
 
 void delta_scan(const Tensor& y, int64_t r_col, int64_t k_col, int64_t v_col, int64_t a_col, int64_t low_col, const Tensor& w2,
                 const Tensor& w0, const Tensor& a_bias, double decay_rate, double key_eps, Tensor& state, const Tensor& cu_q,
-                const Tensor& rows, Tensor& o, int64_t heads, int64_t dim, c10::optional<Tensor> status) {
+                const Tensor& rows, Tensor& o, int64_t heads, int64_t dim, c10::optional<Tensor> status, int64_t most_threads) {
     check_scan(y, state, cu_q, rows, o, heads, dim, dim, "delta_scan");
     check_f32(w2, "w2"); check_f32(w0, "w0"); check_f32(a_bias, "a_bias");
     TORCH_CHECK(w2.dim() == 2 && w2.size(0) == heads * dim && w0.numel() == heads * dim && a_bias.numel() == heads * dim,
@@ -198,7 +198,7 @@ void delta_scan(const Tensor& y, int64_t r_col, int64_t k_col, int64_t v_col, in
     check_launch(vtb::launch_delta_scan(dtype_code(y, "y"), y.data_ptr(), y.size(1), r_col, k_col, v_col, a_col, low_col, rank,
                                         w2.data_ptr<float>(), w0.data_ptr<float>(), a_bias.data_ptr<float>(), (float)decay_rate,
                                         (float)key_eps, state.data_ptr<float>(), state.size(0), cu_q.data_ptr<int>(), rows.data_ptr<int>(),
-                                        rows.numel(), o.data_ptr<float>(), heads, dim, status_ptr(status), stream_of(y)), "delta_scan");
+                                        rows.numel(), o.data_ptr<float>(), heads, dim, (int)most_threads, status_ptr(status), stream_of(y)), "delta_scan");
 }
 
 void check_pages(const Tensor& k_cache, const Tensor& v_cache, const Tensor& ref, int kv_heads, int dim, int v_dim) {
@@ -664,8 +664,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("head_norm_gate", &head_norm_gate, py::arg("o"), py::arg("y"), py::arg("gate_col"), py::arg("weight"),
           py::arg("weight_per_channel"), py::arg("eps"), py::arg("act"), py::arg("out"), py::arg("out_col"), py::arg("out_scale"),
           py::arg("heads"), py::arg("v_dim"), py::arg("token_seq") = py::none());
-    m.def("gla_scan", &gla_scan);
-    m.def("delta_scan", &delta_scan);
+    m.def("gla_scan", &gla_scan, py::arg("y"), py::arg("q_col"), py::arg("k_col"), py::arg("v_col"), py::arg("low_col"), py::arg("a2"),
+          py::arg("a2_bias"), py::arg("inv_tau"), py::arg("q_scale"), py::arg("state"), py::arg("cu_q"), py::arg("rows"), py::arg("o"),
+          py::arg("heads"), py::arg("dim"), py::arg("v_dim"), py::arg("status") = py::none(), py::arg("most_threads") = 0);
+    m.def("delta_scan", &delta_scan, py::arg("y"), py::arg("r_col"), py::arg("k_col"), py::arg("v_col"), py::arg("a_col"), py::arg("low_col"),
+          py::arg("w2"), py::arg("w0"), py::arg("a_bias"), py::arg("decay_rate"), py::arg("key_eps"), py::arg("state"), py::arg("cu_q"),
+          py::arg("rows"), py::arg("o"), py::arg("heads"), py::arg("dim"), py::arg("status") = py::none(), py::arg("most_threads") = 0);
     m.def("attention_prepare", &attention_prepare);
     m.def("attention_general", &attention_general);
     m.def("silu_mul", &silu_mul, py::arg("gu"), py::arg("out"), py::arg("interleave") = 0);

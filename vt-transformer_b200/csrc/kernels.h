@@ -37,17 +37,19 @@ cudaError_t launch_polynorm(int dtype, const void* z, const float* coef, float e
 // Gated linear attention over the tokens of every (sequence, head) in order (recurrent.cu).  y [tokens, stride] holds
 // q, k [heads * dim], v [heads * v_dim] and the low-rank gate's input [rank] at the given columns; a2 [heads * dim,
 // rank] and a2_bias are float; state [state_rows, heads, dim, v_dim] float is read at rows[sequence] and left as after
-// the sequence's last token; out [tokens, heads * v_dim] float.  A sequence without tokens is left alone.
+// the sequence's last token; out [tokens, heads * v_dim] float.  A sequence without tokens is left alone.  most_threads > 0
+// says that the step is a long walk of few sequences: CTAs of 256 threads, a head's column blocks spread over several
+// CTAs; it changes no result.
 cudaError_t launch_gla_scan(int dtype, const void* y, int stride, int q_col, int k_col, int v_col, int low_col, int rank,
                             const float* a2, const float* a2_bias, float inv_tau, float q_scale, float* state,
                             int state_rows, const int* cu_q, const int* rows, int n_seqs, float* out, int heads, int dim,
-                            int v_dim, int* status, cudaStream_t stream);
+                            int v_dim, int most_threads, int* status, cudaStream_t stream);
 // The generalized delta rule in the same manner; a_col: the removal rate's projection, low_col: the decay's low-rank
 // input (tanh is applied to it), w2 [heads * dim, rank], w0 and a_bias float; state [state_rows, heads, dim, dim].
 cudaError_t launch_delta_scan(int dtype, const void* y, int stride, int r_col, int k_col, int v_col, int a_col, int low_col,
                               int rank, const float* w2, const float* w0, const float* a_bias, float decay_rate,
                               float key_eps, float* state, int state_rows, const int* cu_q, const int* rows, int n_seqs,
-                              float* out, int heads, int dim, int* status, cudaStream_t stream);
+                              float* out, int heads, int dim, int most_threads, int* status, cudaStream_t stream);
 // out[t, out_col + h v_dim + i] = out_scale * o[t, h, i] * rsqrt(mean_i o[t, h, :]^2 + eps) * w * act(y[t, gate_col + h v_dim + i]);
 // w = weight[i], or weight[h v_dim + i] with weight_per_channel; act 0: silu, 1: sigmoid.  token_seq (may be null): rows
 // of padding tokens (< 0) become zero.

@@ -19,7 +19,10 @@ namespace vtb {
 namespace {
 
 constexpr int kScanCols = 32;     // columns of the state a warp owns
-// most threads of a CTA, by the rows a thread keeps in registers
+// Most threads of a CTA, by the rows a thread keeps in registers.  A CTA that holds all of a head's columns forms the
+// gates once for all of them, which is what a step of many sequences with a token each wants; a long walk of few
+// sequences wants the head's column blocks on several SMs instead (each then forms the gates again, and issues a
+// quarter of the walk's instructions): the caller bounds the threads by the step's shape (`most_threads`).
 constexpr int scan_threads(int kd) { return kd <= 32 ? 1024 : (kd <= 64 ? 512 : 256); }
 constexpr int kScanTokens = 16;   // tokens staged in shared memory at once
 // values of a token that a thread fetches through its fixed shares (the more threads a CTA has, the fewer each needs)
@@ -43,6 +46,7 @@ struct ScanArgs {
     float* out;                   // [tokens, heads * v_dim]
     int heads, dim, v_dim, groups;
     int col_blocks;               // warps of columns in a CTA
+    int most_threads;             // > 0: the step is a long walk of few sequences (CTAs of 256 threads); 0: the kernel's own bound
     int* status;
 };
 
@@ -58,8 +62,9 @@ __device__ __forceinline__ float sigmoid(float z) { return 1.f / (1.f + expf(-z)
 // threads fetch the batch's projections (each thread the same columns of every token, four tokens' loads in flight at
 // once), form decay, removal rate and unit key from them once for all columns, and then walk the batch's tokens out of
 // shared memory.
-template <typename T, int KD, bool Delta>
-__global__ void __launch_bounds__(scan_threads(KD), 1)
+// Walk: the variant for long walks of few sequences, compiled for CTAs of 256 threads (and the registers they may have).
+template <typename T, int KD, bool Delta, bool Walk>
+__global__ void __launch_bounds__(Walk ? 256 : scan_threads(KD), 1)
 scan_kernel(const ScanArgs a) {
     extern __shared__ __align__(16) float smem[];
     pdl_launch();
@@ -302,14 +307,15 @@ scan_kernel(const ScanArgs a) {
     }
 }
 
-template <typename T, int KD, bool Delta>
+template <typename T, int KD, bool Delta, bool Walk>
 cudaError_t launch_scan_kd(ScanArgs a, int n_seqs, cudaStream_t stream) {
     static std::atomic<unsigned long long> done{0};
     const int G = a.groups, dim_p = G * KD;
     // as many warps of columns a CTA as the head has, within the CTA's threads
     const int col_warps = (a.v_dim + kScanCols - 1) / kScanCols;
     // (a group of warps that meets inside a token has a barrier of its own, of which a CTA has 15)
-    const int most = max(1, min(scan_threads(KD) / (kScanCols * G), G > 1 ? 15 : 32));
+    const int threads = Walk ? min(256, scan_threads(KD)) : scan_threads(KD);
+    const int most = max(1, min(threads / (kScanCols * G), G > 1 ? 15 : 32));
     const int ctas = (col_warps + most - 1) / most;                       // CTAs a head, with its warps of columns spread evenly
     a.col_blocks = (col_warps + ctas - 1) / ctas;
     const int cols = a.col_blocks * kScanCols;
@@ -320,10 +326,10 @@ cudaError_t launch_scan_kd(ScanArgs a, int n_seqs, cudaStream_t stream) {
     constexpr int kMostBytes = 200 * 1024;
     if (bytes > kMostBytes) return cudaErrorInvalidValue;
     // the limit is set once for each device, so it is the most any launch may ask for, not what this one asks for
-    cudaError_t e = allow_dynamic_smem(scan_kernel<T, KD, Delta>, kMostBytes, done);
+    cudaError_t e = allow_dynamic_smem(scan_kernel<T, KD, Delta, Walk>, kMostBytes, done);
     if (e != cudaSuccess) return e;
     dim3 grid(n_seqs, a.heads, (col_warps + a.col_blocks - 1) / a.col_blocks), block(kScanCols, G, a.col_blocks);
-    return launch(scan_kernel<T, KD, Delta>, grid, block, bytes, stream, a);
+    return launch(scan_kernel<T, KD, Delta, Walk>, grid, block, bytes, stream, a);
 }
 
 template <typename T, bool Delta>
@@ -334,10 +340,11 @@ cudaError_t launch_scan_t(ScanArgs a, int n_seqs, cudaStream_t stream) {
     const int kd = a.dim <= 128 ? 16 : (a.dim <= 256 ? 32 : (a.dim <= 512 ? 64 : 128));
     a.groups = (a.dim + kd - 1) / kd;
     if (a.groups > 8) return cudaErrorInvalidValue;
-    if (kd == 16) return launch_scan_kd<T, 16, Delta>(a, n_seqs, stream);
-    if (kd == 32) return launch_scan_kd<T, 32, Delta>(a, n_seqs, stream);
-    if (kd == 64) return launch_scan_kd<T, 64, Delta>(a, n_seqs, stream);
-    return launch_scan_kd<T, 128, Delta>(a, n_seqs, stream);
+    const bool walk = a.most_threads > 0;
+    if (kd == 16) return walk ? launch_scan_kd<T, 16, Delta, true>(a, n_seqs, stream) : launch_scan_kd<T, 16, Delta, false>(a, n_seqs, stream);
+    if (kd == 32) return walk ? launch_scan_kd<T, 32, Delta, true>(a, n_seqs, stream) : launch_scan_kd<T, 32, Delta, false>(a, n_seqs, stream);
+    if (kd == 64) return walk ? launch_scan_kd<T, 64, Delta, true>(a, n_seqs, stream) : launch_scan_kd<T, 64, Delta, false>(a, n_seqs, stream);
+    return launch_scan_kd<T, 128, Delta, false>(a, n_seqs, stream);
 }
 
 }  // namespace
@@ -345,20 +352,20 @@ cudaError_t launch_scan_t(ScanArgs a, int n_seqs, cudaStream_t stream) {
 cudaError_t launch_gla_scan(int dtype, const void* y, int stride, int q_col, int k_col, int v_col, int low_col, int rank,
                             const float* a2, const float* a2_bias, float inv_tau, float q_scale, float* state,
                             int state_rows, const int* cu_q, const int* rows, int n_seqs, float* out, int heads, int dim,
-                            int v_dim, int* status, cudaStream_t stream) {
+                            int v_dim, int most_threads, int* status, cudaStream_t stream) {
     if (n_seqs == 0) return cudaSuccess;
     ScanArgs a = {y, stride, q_col, k_col, v_col, 0, low_col, rank, a2, a2_bias, nullptr, inv_tau, q_scale, state,
-                  state_rows, cu_q, rows, out, heads, dim, v_dim, 1, 1, status};
+                  state_rows, cu_q, rows, out, heads, dim, v_dim, 1, 1, most_threads, status};
     return dtype == kBF16 ? launch_scan_t<__nv_bfloat16, false>(a, n_seqs, stream) : launch_scan_t<float, false>(a, n_seqs, stream);
 }
 
 cudaError_t launch_delta_scan(int dtype, const void* y, int stride, int r_col, int k_col, int v_col, int a_col, int low_col,
                               int rank, const float* w2, const float* w0, const float* a_bias, float decay_rate,
                               float key_eps, float* state, int state_rows, const int* cu_q, const int* rows, int n_seqs,
-                              float* out, int heads, int dim, int* status, cudaStream_t stream) {
+                              float* out, int heads, int dim, int most_threads, int* status, cudaStream_t stream) {
     if (n_seqs == 0) return cudaSuccess;
     ScanArgs a = {y, stride, r_col, k_col, v_col, a_col, low_col, rank, w2, w0, a_bias, decay_rate, key_eps, state,
-                  state_rows, cu_q, rows, out, heads, dim, dim, 1, 1, status};
+                  state_rows, cu_q, rows, out, heads, dim, dim, 1, 1, most_threads, status};
     return dtype == kBF16 ? launch_scan_t<__nv_bfloat16, true>(a, n_seqs, stream) : launch_scan_t<float, true>(a, n_seqs, stream);
 }
 
