@@ -90,7 +90,9 @@ class ModelRunner:
             warnings.warn(line, stacklevel=2)
         limit = spec.max_positions or None
         if max_seq_len is None:
-            max_seq_len = limit or 4096
+            # a model without a limit of positions: a request may grow to 4,096 tokens, or to the whole pool where that is more
+            pool = num_pages * page_size if num_pages is not None else (max_tokens or 0)
+            max_seq_len = limit or max(4096, pool)
         if limit is not None and max_seq_len > limit:
             raise ValueError(f"max_seq_len {max_seq_len} is above the model's {limit} positions")
         if num_pages is None:
