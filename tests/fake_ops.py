@@ -26,11 +26,18 @@ def logits_scale_cap(logits, scale, cap):
         logits.copy_(cap * torch.tanh(logits / cap))
 
 
-def rmsnorm(x, delta, weight, eps, out, rows=None, status=None):
+def _normed_first(d, post_weight, post_eps, post_mult):
+    """A delta that is normed and scaled before it is added."""
+    if post_weight is None:
+        return d
+    return post_mult * post_weight * d * torch.rsqrt((d * d).mean(dim=-1, keepdim=True) + post_eps)
+
+
+def rmsnorm(x, delta, weight, eps, out, rows=None, status=None, post_weight=None, post_eps=0.0, post_mult=1.0):
     idx = torch.arange(x.shape[0]) if rows is None else rows.long()
     v = x[idx]
     if delta is not None:
-        v = v + delta[idx].float()
+        v = v + _normed_first(delta[idx].float(), post_weight, post_eps, post_mult)
         x[idx] = v
     r = torch.rsqrt((v * v).mean(dim=-1, keepdim=True) + eps)
     out.copy_((weight * v * r).to(out.dtype))
@@ -144,11 +151,11 @@ def sample(logits, temperature, top_k, top_p, u, out):
 # ---- the kernels of the layer norm, the general attention, the recurrent mixers and the PolyNorm activation ----
 
 
-def layernorm(x, delta, weight, eps, out, rows=None, status=None):
+def layernorm(x, delta, weight, eps, out, rows=None, status=None, post_weight=None, post_eps=0.0, post_mult=1.0):
     idx = torch.arange(x.shape[0]) if rows is None else rows.long()
     v = x[idx]
     if delta is not None:
-        v = v + delta[idx].float()
+        v = v + _normed_first(delta[idx].float(), post_weight, post_eps, post_mult)
         x[idx] = v
     dev = v - v.mean(dim=-1, keepdim=True)
     out.copy_((weight * dev * torch.rsqrt((dev * dev).mean(dim=-1, keepdim=True) + eps)).to(out.dtype))
@@ -217,12 +224,22 @@ def delta_scan(y, r_col, k_col, v_col, a_col, w1_col, w2, w0, a_bias, decay_rate
 
 
 def attention_prepare(y, q_col, k_col, v_col, positions, token_seq, frequencies, norm_eps, k_cache, v_cache, block_table,
-                      heads, kv_heads, dim, v_dim, store, status=None):
+                      heads, kv_heads, dim, v_dim, store, status=None, v_heads=None, q_weight=None, k_weight=None, norm_first=False):
     T = y.shape[0]
     page_size = k_cache.shape[2]
     live = token_seq >= 0
+    v_heads = kv_heads if v_heads is None else v_heads
 
-    def turn(x):                                   # x [T, n, dim] float
+    def normed(x, w):
+        if norm_eps >= 0:
+            x = x * torch.rsqrt((x * x).mean(dim=-1, keepdim=True) + norm_eps)
+            if w is not None:
+                x = x * w
+        return x
+
+    def turn(x, w=None):                           # x [T, n, dim] float
+        if norm_first:
+            x = normed(x, w)
         if frequencies is not None and frequencies.numel():
             half = frequencies.numel()
             ang = positions.float()[:, None] * frequencies.float()[None, :]
@@ -230,16 +247,16 @@ def attention_prepare(y, q_col, k_col, v_col, positions, token_seq, frequencies,
             a, b = x[..., :half].clone(), x[..., half:2 * half].clone()
             x[..., :half] = a * c - b * s
             x[..., half:2 * half] = b * c + a * s
-        if norm_eps >= 0:
-            x = x * torch.rsqrt((x * x).mean(dim=-1, keepdim=True) + norm_eps)
+        if not norm_first:
+            x = normed(x, w)
         return x
 
-    q = turn(y[:, q_col:q_col + heads * dim].float().view(T, heads, dim).clone())
+    q = turn(y[:, q_col:q_col + heads * dim].float().view(T, heads, dim).clone(), q_weight)
     y[:, q_col:q_col + heads * dim] = q.reshape(T, heads * dim).to(y.dtype)
     if not store:
         return
-    k = turn(y[:, k_col:k_col + kv_heads * dim].float().view(T, kv_heads, dim).clone())
-    v = y[:, v_col:v_col + kv_heads * v_dim].view(T, kv_heads, v_dim)
+    k = turn(y[:, k_col:k_col + kv_heads * dim].float().view(T, kv_heads, dim).clone(), k_weight)
+    v = y[:, v_col:v_col + v_heads * v_dim].view(T, v_heads, v_dim)
     for t in range(T):
         if not bool(live[t]):
             continue
@@ -251,11 +268,11 @@ def attention_prepare(y, q_col, k_col, v_col, positions, token_seq, frequencies,
 
 
 def attention_general(y, q_col, out, out_col, out_scale, k_cache, v_cache, positions, token_seq, block_table, heads, kv_heads,
-                      dim, v_dim, window, chunk, scale, status=None):
+                      dim, v_dim, window, chunk, scale, status=None, keep_first=0, maps=1, lam=0.0, sub_eps=0.0):
     T = y.shape[0]
     page_size = k_cache.shape[2]
     g = heads // kv_heads
-    q = y[:, q_col:q_col + heads * dim].float().view(T, heads, dim)
+    q = y[:, q_col:q_col + heads * maps * dim].float().view(T, heads * maps, dim)
     for t in range(T):
         s = int(token_seq[t])
         if s < 0:
@@ -265,11 +282,53 @@ def attention_general(y, q_col, out, out_col, out_scale, k_cache, v_cache, posit
         first = max(0, p - window + 1) if window > 0 else 0
         if chunk > 0:
             first = max(first, (p // chunk) * chunk)
-        js = torch.arange(first, p + 1)
+        js = torch.cat([torch.arange(0, min(keep_first, first)), torch.arange(first, p + 1)])
         pages = block_table[s, (js // page_size)].long()
         assert bool((pages >= 0).all()), "attention reads a page that is not held"
         keys = k_cache[pages, :, js % page_size, :].float()
         vals = v_cache[pages, :, js % page_size, :].float()
         for h in range(heads):
-            pr = torch.softmax((keys[:, h // g, :] @ q[t, h]) * scale, dim=0)
-            out[t, out_col + h * v_dim:out_col + (h + 1) * v_dim] = (out_scale * (pr @ vals[:, h // g, :])).to(out.dtype)
+            if maps == 1:
+                pr = torch.softmax((keys[:, h // g, :] @ q[t, h]) * scale, dim=0)
+                o = out_scale * (pr @ vals[:, h // g, :])
+            else:
+                a = [torch.softmax((keys[:, (h // g) * 2 + m, :] @ q[t, 2 * h + m]) * scale, dim=0) @ vals[:, h // g, :] for m in range(2)]
+                o = a[0] - lam * a[1]
+                o = out_scale * o * torch.rsqrt((o * o).mean() + sub_eps)
+            out[t, out_col + h * v_dim:out_col + (h + 1) * v_dim] = o.to(out.dtype)
+
+
+def retention_scan(y, q_col, k_col, v_col, decay, k_scale, frequencies, positions, state, cu_q, rows, o, heads, dim, v_dim,
+                   status=None, most_threads=0):
+    yf = y.float()
+    T = y.shape[0]
+
+    def turn(x):
+        if frequencies is not None and frequencies.numel():
+            half = frequencies.numel()
+            ang = positions.float()[:, None] * frequencies.float()[None, :]
+            c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+            a, b = x[..., :half].clone(), x[..., half:2 * half].clone()
+            x[..., :half] = a * c - b * s
+            x[..., half:2 * half] = b * c + a * s
+        return x
+
+    q = turn(yf[:, q_col:q_col + heads * dim].view(T, heads, dim).clone())
+    k = turn(yf[:, k_col:k_col + heads * dim].view(T, heads, dim).clone()) * k_scale
+    v = yf[:, v_col:v_col + heads * v_dim].view(T, heads, v_dim)
+    for row, a, b in _sequences(cu_q, rows):
+        S = state[row].clone()
+        for t in range(a, b):
+            S = decay[:, None, None] * S + k[t][:, :, None] * v[t][:, None, :]
+            o[t] = torch.einsum("hdv,hd->hv", S, q[t]).reshape(-1)
+        state[row] = S
+
+
+def route_experts(logits, top, act, inter):
+    T, n = logits.shape
+    w = torch.zeros((T, n), dtype=torch.float32)
+    for t in range(T):
+        order = sorted(range(n), key=lambda e: (-float(logits[t, e]), e))[:top]
+        w[t, order] = torch.softmax(logits[t, order], dim=0)
+    scaled = act[:, :n * inter].float().view(T, n, inter) * w[:, :, None]
+    act[:, :n * inter] = torch.where(w[:, :, None] > 0, scaled, torch.zeros_like(scaled)).reshape(T, n * inter).to(act.dtype)

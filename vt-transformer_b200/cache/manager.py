@@ -149,7 +149,8 @@ class CacheManager:
                 for layout, slots in by_layout.items()]
         # the bookkeeping (rows, lengths, free lists, block tables) is the C++ object; the tensors stay here
         self.book = _host().CacheBook(page_size, max_requests, max_seq_len,
-                                      [(-1 if layout.window is None else int(layout.window), n) for layout, _, n in plan])
+                                      [(-1 if layout.window is None else int(layout.window), n, int(layout.keep_first))
+                                       for layout, _, n in plan])
         for layout, slots, n in plan:
             tensors = None
             if allocate:

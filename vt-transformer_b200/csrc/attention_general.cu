@@ -1,6 +1,8 @@
 // The general attention: values of another size than keys, a rotation of the first dimensions of a head only with
 // the angle formed where it is used, q and k divided by their root mean square after the rotation, and a mask of
-// chunks beside the causal one and the window.
+// chunks beside the causal one and the window, first tokens that stay visible beside a window, a norm of q and k with a
+// weight before the rotation, and two maps of queries and keys a head over one set of values whose results are
+// subtracted and normed (differential attention).
 //
 // Two kernels.  `attention_prepare` (one block a token, one warp a head): rotation of pairs (i, i + half) by
 // position * frequency[i] (a 32-bit product, precise sine and cosine), the norm over the head in 32-bit, q written
@@ -24,7 +26,8 @@ attention_prepare_kernel(T* __restrict__ y, int stride, int q_col, int k_col, in
                          const int* __restrict__ token_seq, const float* __restrict__ freq, int half, float norm_eps,
                          T* __restrict__ k_cache, T* __restrict__ v_cache, const int* __restrict__ block_table,
                          int table_stride, int n_seqs, int n_pages, int heads, int kv_heads, int dim, int v_dim,
-                         int page_size, int store, int* status) {
+                         int page_size, int store, int* status, int v_heads, const float* __restrict__ q_weight,
+                         const float* __restrict__ k_weight, int norm_first) {
     __shared__ float head[kPrepareWarps][32 * kMaxPerLane];
     pdl_launch();
     const int t = blockIdx.x;
@@ -56,6 +59,15 @@ attention_prepare_kernel(T* __restrict__ y, int stride, int q_col, int k_col, in
         T* src = is_q ? row + q_col + u * dim : row + k_col + (u - heads) * dim;
         for (int i = lane; i < dim; i += 32) hv[i] = to_float(src[i]);
         __syncwarp();
+        const float* w = is_q ? q_weight : k_weight;           // the norm's weight [dim], or none
+        if (norm_first && norm_eps >= 0.f) {
+            // the norm comes before the rotation: the head is normed where it lies, then turned
+            float s0 = 0.f;
+            for (int i = lane; i < dim; i += 32) s0 = fmaf(hv[i], hv[i], s0);
+            const float sc = rsqrtf(warp_sum(s0) / (float)dim + norm_eps);
+            for (int i = lane; i < dim; i += 32) hv[i] = hv[i] * sc * (w ? w[i] : 1.f);
+            __syncwarp();
+        }
         float x[kMaxPerLane];
         float ss = 0.f;
 #pragma unroll
@@ -76,19 +88,20 @@ attention_prepare_kernel(T* __restrict__ y, int stride, int q_col, int k_col, in
             ss = fmaf(v, v, ss);
         }
         float scale = 1.f;
-        if (norm_eps >= 0.f) scale = rsqrtf(warp_sum(ss) / (float)dim + norm_eps);
+        const bool after = !norm_first && norm_eps >= 0.f;
+        if (after) scale = rsqrtf(warp_sum(ss) / (float)dim + norm_eps);
         T* dst = is_q ? src : k_cache + (((size_t)page * kv_heads + (u - heads)) * page_size + slot) * dim;
 #pragma unroll
         for (int r = 0; r < kMaxPerLane; ++r) {
             const int i = lane + 32 * r;
-            if (i < dim) dst[i] = from_float<T>(x[r] * scale);
+            if (i < dim) dst[i] = from_float<T>(x[r] * scale * ((after && w) ? w[i] : 1.f));
         }
         __syncwarp();
     }
     if (!store) return;
-    for (int e = threadIdx.x; e < kv_heads * v_dim; e += blockDim.x) {
+    for (int e = threadIdx.x; e < v_heads * v_dim; e += blockDim.x) {
         const int h = e / v_dim, i = e % v_dim;
-        v_cache[(((size_t)page * kv_heads + h) * page_size + slot) * v_dim + i] = row[v_col + e];
+        v_cache[(((size_t)page * v_heads + h) * page_size + slot) * v_dim + i] = row[v_col + e];
     }
 }
 
@@ -96,32 +109,38 @@ cudaError_t launch_attention_prepare(int dtype, void* y, int stride, int q_col, 
                                      const int* token_seq, const float* freq, int half, float norm_eps, void* k_cache,
                                      void* v_cache, const int* block_table, int table_stride, int n_seqs, int n_pages,
                                      int n_tokens, int heads, int kv_heads, int dim, int v_dim, int page_size, int store,
-                                     int* status, cudaStream_t stream) {
+                                     int* status, int v_heads, const float* q_weight, const float* k_weight, int norm_first,
+                                     cudaStream_t stream) {
     if (n_tokens == 0) return cudaSuccess;
     if (dim > 32 * kMaxPerLane || 2 * half > dim) return cudaErrorInvalidValue;
     if (dtype == kBF16)
         return launch(attention_prepare_kernel<__nv_bfloat16>, n_tokens, 32 * kPrepareWarps, 0, stream, (__nv_bfloat16*)y, stride,
                       q_col, k_col, v_col, positions, token_seq, freq, half, norm_eps, (__nv_bfloat16*)k_cache,
                       (__nv_bfloat16*)v_cache, block_table, table_stride, n_seqs, n_pages, heads, kv_heads, dim, v_dim,
-                      page_size, store, status);
+                      page_size, store, status, v_heads, q_weight, k_weight, norm_first);
     return launch(attention_prepare_kernel<float>, n_tokens, 32 * kPrepareWarps, 0, stream, (float*)y, stride, q_col, k_col,
                   v_col, positions, token_seq, freq, half, norm_eps, (float*)k_cache, (float*)v_cache, block_table,
-                  table_stride, n_seqs, n_pages, heads, kv_heads, dim, v_dim, page_size, store, status);
+                  table_stride, n_seqs, n_pages, heads, kv_heads, dim, v_dim, page_size, store, status, v_heads, q_weight, k_weight,
+                  norm_first);
 }
 
 // One warp for a (token, head).  The visible keys are taken 32 at a time, a lane a key: the lane forms its key's whole
 // score from q in shared memory (no exchange between lanes for a score), the block's maximum and sum are found once,
 // and the block's values are added with a lane owning dimensions i, i + 32, ... of the result.  The blocks start at the
 // first visible key, which depends on the token's position alone, so a token's result does not depend on the step.
-template <typename T, bool Vec>
+// With a window and `keep_first`, the keys at positions below keep_first that the window has passed come first, in
+// blocks that start at key 0.  MAPS 2: the head has two queries and its head of values two heads of keys; a lane forms
+// both scores of its key, each map keeps a maximum, a sum and a result of its own over the same values (read once),
+// and the end is o = a_1 - lam a_2, divided by its root mean square.
+template <typename T, bool Vec, int MAPS>
 __global__ void __launch_bounds__(128)
 attention_general_kernel(const T* __restrict__ y, int stride, int q_col, T* __restrict__ out, int out_stride, int out_col,
                          float out_scale, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
                          const int* __restrict__ positions, const int* __restrict__ token_seq,
                          const int* __restrict__ block_table, int table_stride, int n_seqs, int n_pages, int n_tokens,
                          int heads, int kv_heads, int dim, int v_dim, int page_size, int window, int chunk, float scale,
-                         int* status) {
-    __shared__ __align__(16) float qs[4][32 * kMaxPerLane];
+                         int* status, int keep_first, float lam, float sub_eps) {
+    __shared__ __align__(16) float qs[4][MAPS * 32 * kMaxPerLane];
     pdl_launch();
     pdl_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -142,72 +161,117 @@ attention_general_kernel(const T* __restrict__ y, int stride, int q_col, T* __re
     const int kvh = h / (heads / kv_heads);
     const int* table = block_table + (size_t)seq * table_stride;
     float* q = qs[warp];
-    const T* qp = y + (size_t)t * stride + q_col + (size_t)h * dim;
-    for (int i = lane; i < dim; i += 32) q[i] = to_float(qp[i]) * scale;
+    const T* qp = y + (size_t)t * stride + q_col + (size_t)h * MAPS * dim;
+    const int dim_s = (dim + 3) & ~3;                              // a map's query starts on a 16-byte boundary
+    for (int i = lane; i < MAPS * dim; i += 32) q[(i / dim) * dim_s + i % dim] = to_float(qp[i]) * scale;
     __syncwarp();
 
-    float acc[kMaxPerLane];
+    float acc[MAPS][kMaxPerLane];
+    float mx[MAPS], sum[MAPS];
 #pragma unroll
-    for (int r = 0; r < kMaxPerLane; ++r) acc[r] = 0.f;
-    float mx = -INFINITY, sum = 0.f;
-    int first = (window > 0) ? max(0, pos - window + 1) : 0;
-    if (chunk > 0) first = max(first, (pos / chunk) * chunk);      // chunks are counted from position 0 of the sequence
-    for (int j0 = first; j0 <= pos; j0 += 32) {
-        const int j = j0 + lane;
-        bool live = j <= pos;
-        int at = 0;                                                // the key's row in the pages
-        if (live) {
-            const int page = table[j / page_size];
-            if (page < 0 || page >= n_pages) {
-                set_status(status, kStatusBadPage, page);
-                live = false;
-            } else {
-                at = (page * kv_heads + kvh) * page_size + (j % page_size);
-            }
-        }
-        float s = -INFINITY;
-        if (live) {
-            const T* kp = k_cache + (size_t)at * dim;
-            float part[4] = {0.f, 0.f, 0.f, 0.f};
-            if (Vec) {
-                for (int i = 0; i < dim; i += 8) {
-                    float k8[8];
-                    Vec8<T>::load(kp + i, k8);
-                    const float4 qa = *reinterpret_cast<const float4*>(q + i), qb = *reinterpret_cast<const float4*>(q + i + 4);
-                    part[0] = fmaf(qa.x, k8[0], part[0]); part[1] = fmaf(qa.y, k8[1], part[1]);
-                    part[2] = fmaf(qa.z, k8[2], part[2]); part[3] = fmaf(qa.w, k8[3], part[3]);
-                    part[0] = fmaf(qb.x, k8[4], part[0]); part[1] = fmaf(qb.y, k8[5], part[1]);
-                    part[2] = fmaf(qb.z, k8[6], part[2]); part[3] = fmaf(qb.w, k8[7], part[3]);
+    for (int m = 0; m < MAPS; ++m) {
+        mx[m] = -INFINITY;
+        sum[m] = 0.f;
+#pragma unroll
+        for (int r = 0; r < kMaxPerLane; ++r) acc[m][r] = 0.f;
+    }
+    const int first = first_visible_key(pos, window, chunk);
+    // the kept first tokens that the window has passed (none without a window, and none beside chunks)
+    const int kept = (window > 0 && chunk <= 0) ? min(keep_first, first) : 0;
+    for (int part = 0; part < 2; ++part) {
+        const int lo = part == 0 ? 0 : first, hi = part == 0 ? kept : pos + 1;
+        for (int j0 = lo; j0 < hi; j0 += 32) {
+            const int j = j0 + lane;
+            bool live = j < hi;
+            int at_k = 0, at_v = 0;                                // the key's (map 0) and the value's row in the pages
+            if (live) {
+                const int page = table[j / page_size];
+                if (page < 0 || page >= n_pages) {
+                    set_status(status, kStatusBadPage, page);
+                    live = false;
+                } else {
+                    at_k = (page * kv_heads * MAPS + kvh * MAPS) * page_size + (j % page_size);
+                    at_v = (page * kv_heads + kvh) * page_size + (j % page_size);
                 }
-            } else {
-                for (int i = 0; i < dim; ++i) part[i & 3] = fmaf(q[i], to_float(kp[i]), part[i & 3]);
             }
-            s = (part[0] + part[1]) + (part[2] + part[3]);
-        }
-        const float new_mx = fmaxf(mx, warp_max(s));              // the first block holds the token's own key: finite
-        const float corr = expf(mx - new_mx);                      // 0 at the first block (mx = -inf)
-        const float p = live ? expf(s - new_mx) : 0.f;
-        sum = sum * corr + warp_sum(p);
-        mx = new_mx;
+            float s[MAPS];
 #pragma unroll
-        for (int r = 0; r < kMaxPerLane; ++r) acc[r] *= corr;
-        const int n = min(32, pos - j0 + 1);
-        for (int jj = 0; jj < n; ++jj) {
-            const float pj = __shfl_sync(0xffffffffu, p, jj);
-            const int aj = __shfl_sync(0xffffffffu, at, jj);
-            const T* vp = v_cache + (size_t)aj * v_dim;
+            for (int m = 0; m < MAPS; ++m) {
+                s[m] = -INFINITY;
+                if (!live) continue;
+                const T* kp = k_cache + (size_t)(at_k + m * page_size) * dim;
+                const float* qm = q + m * dim_s;
+                float part4[4] = {0.f, 0.f, 0.f, 0.f};
+                if (Vec) {
+                    for (int i = 0; i < dim; i += 8) {
+                        float k8[8];
+                        Vec8<T>::load(kp + i, k8);
+                        const float4 qa = *reinterpret_cast<const float4*>(qm + i), qb = *reinterpret_cast<const float4*>(qm + i + 4);
+                        part4[0] = fmaf(qa.x, k8[0], part4[0]); part4[1] = fmaf(qa.y, k8[1], part4[1]);
+                        part4[2] = fmaf(qa.z, k8[2], part4[2]); part4[3] = fmaf(qa.w, k8[3], part4[3]);
+                        part4[0] = fmaf(qb.x, k8[4], part4[0]); part4[1] = fmaf(qb.y, k8[5], part4[1]);
+                        part4[2] = fmaf(qb.z, k8[6], part4[2]); part4[3] = fmaf(qb.w, k8[7], part4[3]);
+                    }
+                } else {
+                    for (int i = 0; i < dim; ++i) part4[i & 3] = fmaf(qm[i], to_float(kp[i]), part4[i & 3]);
+                }
+                s[m] = (part4[0] + part4[1]) + (part4[2] + part4[3]);
+            }
+            float p[MAPS];
 #pragma unroll
-            for (int r = 0; r < kMaxPerLane; ++r) {
-                const int i = lane + 32 * r;
-                if (i < v_dim) acc[r] = fmaf(pj, to_float(vp[i]), acc[r]);
+            for (int m = 0; m < MAPS; ++m) {
+                const float new_mx = fmaxf(mx[m], warp_max(s[m]));     // a block holds at least one visible key: finite
+                const float corr = expf(mx[m] - new_mx);               // 0 at the first block (mx = -inf)
+                p[m] = live ? expf(s[m] - new_mx) : 0.f;
+                sum[m] = sum[m] * corr + warp_sum(p[m]);
+                mx[m] = new_mx;
+#pragma unroll
+                for (int r = 0; r < kMaxPerLane; ++r) acc[m][r] *= corr;
+            }
+            const int n = min(32, hi - j0);
+            for (int jj = 0; jj < n; ++jj) {
+                float pj[MAPS];
+#pragma unroll
+                for (int m = 0; m < MAPS; ++m) pj[m] = __shfl_sync(0xffffffffu, p[m], jj);
+                const int aj = __shfl_sync(0xffffffffu, at_v, jj);
+                const T* vp = v_cache + (size_t)aj * v_dim;
+#pragma unroll
+                for (int r = 0; r < kMaxPerLane; ++r) {
+                    const int i = lane + 32 * r;
+                    if (i < v_dim) {
+                        const float v = to_float(vp[i]);
+#pragma unroll
+                        for (int m = 0; m < MAPS; ++m) acc[m][r] = fmaf(pj[m], v, acc[m][r]);
+                    }
+                }
             }
         }
     }
-    const float inv = sum > 0.f ? out_scale / sum : 0.f;
+    if (MAPS == 1) {
+        const float inv = sum[0] > 0.f ? out_scale / sum[0] : 0.f;
+#pragma unroll
+        for (int r = 0; r < kMaxPerLane; ++r) {
+            const int i = lane + 32 * r;
+            if (i < v_dim) o[i] = from_float<T>(acc[0][r] * inv);
+        }
+        return;
+    }
+    // the difference of the two maps, divided by its root mean square over the head's values
+    const float inv0 = sum[0] > 0.f ? 1.f / sum[0] : 0.f;
+    const float inv1 = sum[MAPS - 1] > 0.f ? 1.f / sum[MAPS - 1] : 0.f;
+    float d[kMaxPerLane];
+    float ss = 0.f;
 #pragma unroll
     for (int r = 0; r < kMaxPerLane; ++r) {
         const int i = lane + 32 * r;
-        if (i < v_dim) o[i] = from_float<T>(acc[r] * inv);
+        d[r] = i < v_dim ? acc[0][r] * inv0 - lam * (acc[MAPS - 1][r] * inv1) : 0.f;
+        ss = fmaf(d[r], d[r], ss);
+    }
+    const float rs = rsqrtf(warp_sum(ss) / (float)v_dim + sub_eps) * out_scale;
+#pragma unroll
+    for (int r = 0; r < kMaxPerLane; ++r) {
+        const int i = lane + 32 * r;
+        if (i < v_dim) o[i] = from_float<T>(d[r] * rs);
     }
 }
 
@@ -216,32 +280,36 @@ static cudaError_t launch_attention_general_t(const T* y, int stride, int q_col,
                                               const T* k_cache, const T* v_cache, const int* positions, const int* token_seq,
                                               const int* block_table, int table_stride, int n_seqs, int n_pages, int n_tokens,
                                               int heads, int kv_heads, int dim, int v_dim, int page_size, int window, int chunk,
-                                              float scale, int* status, cudaStream_t stream) {
+                                              float scale, int* status, int keep_first, int maps, float lam, float sub_eps,
+                                              cudaStream_t stream) {
     const long long pairs = (long long)n_tokens * heads;
     const int blocks = (int)((pairs + 3) / 4);
     // a key's row is read in 16-byte pieces where every row starts on such a boundary
     const bool vec = dim % 8 == 0 && (reinterpret_cast<uintptr_t>(k_cache) & 15) == 0;
-    auto kernel = vec ? attention_general_kernel<T, true> : attention_general_kernel<T, false>;
+    auto kernel = maps == 2 ? (vec ? attention_general_kernel<T, true, 2> : attention_general_kernel<T, false, 2>)
+                            : (vec ? attention_general_kernel<T, true, 1> : attention_general_kernel<T, false, 1>);
     return launch(kernel, blocks, 128, 0, stream, y, stride, q_col, out, out_stride, out_col, out_scale, k_cache, v_cache, positions,
                   token_seq, block_table, table_stride, n_seqs, n_pages, n_tokens, heads, kv_heads, dim, v_dim, page_size, window,
-                  chunk, scale, status);
+                  chunk, scale, status, keep_first, lam, sub_eps);
 }
 
 cudaError_t launch_attention_general(int dtype, const void* y, int stride, int q_col, void* out, int out_stride, int out_col,
                                      float out_scale, const void* k_cache, const void* v_cache, const int* positions,
                                      const int* token_seq, const int* block_table, int table_stride, int n_seqs, int n_pages,
                                      int n_tokens, int heads, int kv_heads, int dim, int v_dim, int page_size, int window,
-                                     int chunk, float scale, int* status, cudaStream_t stream) {
+                                     int chunk, float scale, int* status, int keep_first, int maps, float lam, float sub_eps,
+                                     cudaStream_t stream) {
     if (n_tokens == 0) return cudaSuccess;
-    if (dim > 32 * kMaxPerLane || v_dim > 32 * kMaxPerLane) return cudaErrorInvalidValue;
+    if (dim > 32 * kMaxPerLane || v_dim > 32 * kMaxPerLane || (maps != 1 && maps != 2)) return cudaErrorInvalidValue;
     if (dtype == kBF16)
         return launch_attention_general_t((const __nv_bfloat16*)y, stride, q_col, (__nv_bfloat16*)out, out_stride, out_col, out_scale,
                                           (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, positions, token_seq,
                                           block_table, table_stride, n_seqs, n_pages, n_tokens, heads, kv_heads, dim, v_dim,
-                                          page_size, window, chunk, scale, status, stream);
+                                          page_size, window, chunk, scale, status, keep_first, maps, lam, sub_eps, stream);
     return launch_attention_general_t((const float*)y, stride, q_col, (float*)out, out_stride, out_col, out_scale, (const float*)k_cache,
                                       (const float*)v_cache, positions, token_seq, block_table, table_stride, n_seqs, n_pages,
-                                      n_tokens, heads, kv_heads, dim, v_dim, page_size, window, chunk, scale, status, stream);
+                                      n_tokens, heads, kv_heads, dim, v_dim, page_size, window, chunk, scale, status, keep_first,
+                                      maps, lam, sub_eps, stream);
 }
 
 }  // namespace vtb

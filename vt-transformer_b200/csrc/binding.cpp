@@ -66,7 +66,8 @@ void logits_scale_cap(Tensor& logits, double scale, double cap) {
 }
 
 void norm_rows(bool center, Tensor& x, c10::optional<Tensor> delta, const Tensor& weight, double eps, Tensor& out,
-               c10::optional<Tensor> rows, c10::optional<Tensor> status) {
+               c10::optional<Tensor> rows, c10::optional<Tensor> status, c10::optional<Tensor> post_weight, double post_eps,
+               double post_mult) {
     check_f32(x, "x"); check_f32(weight, "weight"); check_cuda(out, "out");
     TORCH_CHECK(x.dim() == 2 && out.dim() == 2, "rmsnorm: x and out must be 2-d");
     const int hidden = x.size(1);
@@ -97,21 +98,32 @@ void norm_rows(bool center, Tensor& x, c10::optional<Tensor> delta, const Tensor
         n_rows = rows->numel();
     }
     TORCH_CHECK(out.size(0) == n_rows, "rmsnorm: out must have one row for each normed row");
+    const float* pw = nullptr;
+    if (post_weight.has_value()) {
+        // the delta is normed (root mean square, this weight, post_mult) before it is added
+        check_f32(*post_weight, "post_weight");
+        TORCH_CHECK(post_weight->numel() == hidden, "rmsnorm: the weight of the delta's norm must match hidden size");
+        TORCH_CHECK(dp != nullptr || pp != nullptr, "rmsnorm: a norm of the delta without a delta");
+        pw = post_weight->data_ptr<float>();
+    }
     c10::cuda::CUDAGuard guard(x.device());
     check_launch((center ? vtb::launch_layernorm : vtb::launch_rmsnorm)(code, x.data_ptr<float>(), dp, pp, n_parts,
                                                                         weight.data_ptr<float>(), (float)eps, out.data_ptr(), rp,
-                                                                        n_rows, x.size(0), hidden, status_ptr(status),
+                                                                        n_rows, x.size(0), hidden, status_ptr(status), pw,
+                                                                        (float)post_eps, (float)post_mult,
                                                                         stream_of(x)), center ? "layernorm" : "rmsnorm");
 }
 
 void rmsnorm(Tensor& x, c10::optional<Tensor> delta, const Tensor& weight, double eps, Tensor& out,
-             c10::optional<Tensor> rows, c10::optional<Tensor> status) {
-    norm_rows(false, x, delta, weight, eps, out, rows, status);
+             c10::optional<Tensor> rows, c10::optional<Tensor> status, c10::optional<Tensor> post_weight, double post_eps,
+             double post_mult) {
+    norm_rows(false, x, delta, weight, eps, out, rows, status, post_weight, post_eps, post_mult);
 }
 
 void layernorm(Tensor& x, c10::optional<Tensor> delta, const Tensor& weight, double eps, Tensor& out,
-               c10::optional<Tensor> rows, c10::optional<Tensor> status) {
-    norm_rows(true, x, delta, weight, eps, out, rows, status);
+               c10::optional<Tensor> rows, c10::optional<Tensor> status, c10::optional<Tensor> post_weight, double post_eps,
+               double post_mult) {
+    norm_rows(true, x, delta, weight, eps, out, rows, status, post_weight, post_eps, post_mult);
 }
 
 void polynorm(const Tensor& z, const Tensor& coef, double eps, Tensor& out, int64_t n_mean) {
@@ -201,11 +213,12 @@ void delta_scan(const Tensor& y, int64_t r_col, int64_t k_col, int64_t v_col, in
                                         rows.numel(), o.data_ptr<float>(), heads, dim, (int)most_threads, status_ptr(status), stream_of(y)), "delta_scan");
 }
 
-void check_pages(const Tensor& k_cache, const Tensor& v_cache, const Tensor& ref, int kv_heads, int dim, int v_dim) {
+void check_pages(const Tensor& k_cache, const Tensor& v_cache, const Tensor& ref, int kv_heads, int dim, int v_dim, int v_heads = -1) {
     check_cuda(k_cache, "k_cache"); check_cuda(v_cache, "v_cache");
+    if (v_heads < 0) v_heads = kv_heads;
     TORCH_CHECK(k_cache.dim() == 4 && v_cache.dim() == 4 && k_cache.size(0) == v_cache.size(0) && k_cache.size(2) == v_cache.size(2),
                 "cache: k [pages, kv_heads, page_size, dim] and v [pages, kv_heads, page_size, v_dim]");
-    TORCH_CHECK(k_cache.size(1) == kv_heads && v_cache.size(1) == kv_heads && k_cache.size(3) == dim && v_cache.size(3) == v_dim,
+    TORCH_CHECK(k_cache.size(1) == kv_heads && v_cache.size(1) == v_heads && k_cache.size(3) == dim && v_cache.size(3) == v_dim,
                 "cache: kv_heads, dim or v_dim differ");
     TORCH_CHECK(k_cache.scalar_type() == ref.scalar_type() && v_cache.scalar_type() == ref.scalar_type(),
                 "cache: dtype differs from the activations'");
@@ -213,13 +226,19 @@ void check_pages(const Tensor& k_cache, const Tensor& v_cache, const Tensor& ref
 
 void attention_prepare(Tensor& y, int64_t q_col, int64_t k_col, int64_t v_col, const Tensor& positions, const Tensor& token_seq,
                        c10::optional<Tensor> frequencies, double norm_eps, Tensor& k_cache, Tensor& v_cache, const Tensor& block_table,
-                       int64_t heads, int64_t kv_heads, int64_t dim, int64_t v_dim, bool store, c10::optional<Tensor> status) {
+                       int64_t heads, int64_t kv_heads, int64_t dim, int64_t v_dim, bool store, c10::optional<Tensor> status,
+                       int64_t v_heads, c10::optional<Tensor> q_weight, c10::optional<Tensor> k_weight, bool norm_first) {
     check_cuda(y, "y"); check_i32(positions, "positions"); check_i32(token_seq, "token_seq"); check_i32(block_table, "block_table");
     TORCH_CHECK(y.dim() == 2 && positions.numel() == y.size(0) && token_seq.numel() == y.size(0), "attention_prepare: one position and sequence a token");
     TORCH_CHECK(block_table.dim() == 2, "attention_prepare: block_table must be [sequences, stride]");
+    if (v_heads < 0) v_heads = kv_heads;
     check_cols(y, q_col, heads * dim, "attention_prepare (q)"); check_cols(y, k_col, kv_heads * dim, "attention_prepare (k)");
-    check_cols(y, v_col, kv_heads * v_dim, "attention_prepare (v)");
-    check_pages(k_cache, v_cache, y, kv_heads, dim, v_dim);
+    check_cols(y, v_col, v_heads * v_dim, "attention_prepare (v)");
+    check_pages(k_cache, v_cache, y, kv_heads, dim, v_dim, v_heads);
+    const float* qw = nullptr;
+    const float* kw = nullptr;
+    if (q_weight.has_value()) { check_f32(*q_weight, "q_weight"); TORCH_CHECK(q_weight->numel() == dim, "attention_prepare: q_weight [dim]"); qw = q_weight->data_ptr<float>(); }
+    if (k_weight.has_value()) { check_f32(*k_weight, "k_weight"); TORCH_CHECK(k_weight->numel() == dim, "attention_prepare: k_weight [dim]"); kw = k_weight->data_ptr<float>(); }
     const float* fp = nullptr;
     int half = 0;
     if (frequencies.has_value()) {
@@ -234,27 +253,65 @@ void attention_prepare(Tensor& y, int64_t q_col, int64_t k_col, int64_t v_col, c
                                                token_seq.data_ptr<int>(), fp, half, (float)norm_eps, k_cache.data_ptr(), v_cache.data_ptr(),
                                                block_table.data_ptr<int>(), block_table.size(1), block_table.size(0), k_cache.size(0),
                                                y.size(0), heads, kv_heads, dim, v_dim, k_cache.size(2), store ? 1 : 0, status_ptr(status),
-                                               stream_of(y)), "attention_prepare");
+                                               v_heads, qw, kw, norm_first ? 1 : 0, stream_of(y)), "attention_prepare");
 }
 
 void attention_general(const Tensor& y, int64_t q_col, Tensor& out, int64_t out_col, double out_scale, const Tensor& k_cache,
                        const Tensor& v_cache, const Tensor& positions, const Tensor& token_seq, const Tensor& block_table, int64_t heads,
-                       int64_t kv_heads, int64_t dim, int64_t v_dim, int64_t window, int64_t chunk, double scale, c10::optional<Tensor> status) {
+                       int64_t kv_heads, int64_t dim, int64_t v_dim, int64_t window, int64_t chunk, double scale, c10::optional<Tensor> status,
+                       int64_t keep_first, int64_t maps, double lam, double sub_eps) {
     check_cuda(y, "y"); check_cuda(out, "out"); check_i32(positions, "positions"); check_i32(token_seq, "token_seq");
+    TORCH_CHECK(maps == 1 || maps == 2, "attention_general: one map of queries and keys a head, or two");
     check_i32(block_table, "block_table");
     TORCH_CHECK(y.dim() == 2 && out.dim() == 2 && out.size(0) == y.size(0) && out.scalar_type() == y.scalar_type(),
                 "attention_general: y and out [tokens, .] of one dtype");
     TORCH_CHECK(positions.numel() == y.size(0) && token_seq.numel() == y.size(0), "attention_general: one position and sequence a token");
     TORCH_CHECK(block_table.dim() == 2 && heads % kv_heads == 0, "attention_general: block_table [sequences, stride]; heads a multiple of kv_heads");
-    check_cols(y, q_col, heads * dim, "attention_general (q)"); check_cols(out, out_col, heads * v_dim, "attention_general (out)");
-    check_pages(k_cache, v_cache, y, kv_heads, dim, v_dim);
+    check_cols(y, q_col, heads * maps * dim, "attention_general (q)"); check_cols(out, out_col, heads * v_dim, "attention_general (out)");
+    check_pages(k_cache, v_cache, y, kv_heads * maps, dim, v_dim, kv_heads);
     TORCH_CHECK(dim <= 256 && v_dim <= 256, "attention_general: head sizes up to 256");
     c10::cuda::CUDAGuard guard(y.device());
     check_launch(vtb::launch_attention_general(dtype_code(y, "y"), y.data_ptr(), y.size(1), q_col, out.data_ptr(), out.size(1), out_col,
                                                (float)out_scale, k_cache.data_ptr(), v_cache.data_ptr(), positions.data_ptr<int>(),
                                                token_seq.data_ptr<int>(), block_table.data_ptr<int>(), block_table.size(1),
                                                block_table.size(0), k_cache.size(0), y.size(0), heads, kv_heads, dim, v_dim, k_cache.size(2),
-                                               window, chunk, (float)scale, status_ptr(status), stream_of(y)), "attention_general");
+                                               window, chunk, (float)scale, status_ptr(status), keep_first, maps, (float)lam,
+                                               (float)sub_eps, stream_of(y)), "attention_general");
+}
+
+void retention_scan(const Tensor& y, int64_t q_col, int64_t k_col, int64_t v_col, const Tensor& decay, double k_scale,
+                    c10::optional<Tensor> frequencies, const Tensor& positions, Tensor& state, const Tensor& cu_q, const Tensor& rows,
+                    Tensor& o, int64_t heads, int64_t dim, int64_t v_dim, c10::optional<Tensor> status, int64_t most_threads) {
+    check_scan(y, state, cu_q, rows, o, heads, dim, v_dim, "retention_scan");
+    check_f32(decay, "decay"); check_i32(positions, "positions");
+    TORCH_CHECK(decay.numel() == heads, "retention_scan: one decay for each head");
+    TORCH_CHECK(positions.numel() == y.size(0), "retention_scan: one position a token");
+    check_cols(y, q_col, heads * dim, "retention_scan (q)"); check_cols(y, k_col, heads * dim, "retention_scan (k)");
+    check_cols(y, v_col, heads * v_dim, "retention_scan (v)");
+    const float* fp = nullptr;
+    int half = 0;
+    if (frequencies.has_value()) {
+        check_f32(*frequencies, "frequencies");
+        fp = frequencies->data_ptr<float>();
+        half = frequencies->numel();
+        TORCH_CHECK(2 * half <= dim, "retention_scan: the rotation covers more than the head");
+    }
+    c10::cuda::CUDAGuard guard(y.device());
+    check_launch(vtb::launch_retention_scan(dtype_code(y, "y"), y.data_ptr(), y.size(1), q_col, k_col, v_col, decay.data_ptr<float>(),
+                                            (float)k_scale, fp, half, positions.data_ptr<int>(), state.data_ptr<float>(), state.size(0),
+                                            cu_q.data_ptr<int>(), rows.data_ptr<int>(), rows.numel(), o.data_ptr<float>(), heads, dim,
+                                            v_dim, (int)most_threads, status_ptr(status), stream_of(y)), "retention_scan");
+}
+
+void route_experts(const Tensor& logits, int64_t top, Tensor& act, int64_t inter) {
+    check_f32(logits, "logits"); check_cuda(act, "act");
+    TORCH_CHECK(logits.dim() == 2 && act.dim() == 2 && act.size(0) == logits.size(0), "route_experts: logits [tokens, experts], act [tokens, .]");
+    const int experts = logits.size(1);
+    TORCH_CHECK(experts >= 1 && experts <= 1024 && top >= 1 && top <= experts, "route_experts: 1 <= top <= experts <= 1024");
+    TORCH_CHECK(inter >= 0 && experts * inter <= act.size(1), "route_experts: experts * inter columns lie outside act");
+    c10::cuda::CUDAGuard guard(act.device());
+    check_launch(vtb::launch_route_experts(dtype_code(act, "act"), logits.data_ptr<float>(), logits.size(0), experts, top, act.data_ptr(),
+                                           act.size(1), inter, stream_of(act)), "route_experts");
 }
 
 
@@ -656,9 +713,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("scale") = 1.0);
     m.def("logits_scale_cap", &logits_scale_cap, py::arg("logits"), py::arg("scale"), py::arg("cap"));
     m.def("rmsnorm", &rmsnorm, py::arg("x"), py::arg("delta"), py::arg("weight"), py::arg("eps"), py::arg("out"),
-          py::arg("rows") = py::none(), py::arg("status") = py::none());
+          py::arg("rows") = py::none(), py::arg("status") = py::none(), py::arg("post_weight") = py::none(),
+          py::arg("post_eps") = 0.0, py::arg("post_mult") = 1.0);
     m.def("layernorm", &layernorm, py::arg("x"), py::arg("delta"), py::arg("weight"), py::arg("eps"), py::arg("out"),
-          py::arg("rows") = py::none(), py::arg("status") = py::none());
+          py::arg("rows") = py::none(), py::arg("status") = py::none(), py::arg("post_weight") = py::none(),
+          py::arg("post_eps") = 0.0, py::arg("post_mult") = 1.0);
     m.def("polynorm", &polynorm, py::arg("z"), py::arg("coefficients"), py::arg("eps"), py::arg("out"), py::arg("n_mean") = 0);
     m.def("scale_into", &scale_into);
     m.def("head_norm_gate", &head_norm_gate, py::arg("o"), py::arg("y"), py::arg("gate_col"), py::arg("weight"),
@@ -670,8 +729,16 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("delta_scan", &delta_scan, py::arg("y"), py::arg("r_col"), py::arg("k_col"), py::arg("v_col"), py::arg("a_col"), py::arg("low_col"),
           py::arg("w2"), py::arg("w0"), py::arg("a_bias"), py::arg("decay_rate"), py::arg("key_eps"), py::arg("state"), py::arg("cu_q"),
           py::arg("rows"), py::arg("o"), py::arg("heads"), py::arg("dim"), py::arg("status") = py::none(), py::arg("most_threads") = 0);
-    m.def("attention_prepare", &attention_prepare);
-    m.def("attention_general", &attention_general);
+    m.def("attention_prepare", &attention_prepare, py::arg("y"), py::arg("q_col"), py::arg("k_col"), py::arg("v_col"), py::arg("positions"),
+          py::arg("token_seq"), py::arg("frequencies"), py::arg("norm_eps"), py::arg("k_cache"), py::arg("v_cache"), py::arg("block_table"),
+          py::arg("heads"), py::arg("kv_heads"), py::arg("dim"), py::arg("v_dim"), py::arg("store"), py::arg("status") = py::none(),
+          py::arg("v_heads") = -1, py::arg("q_weight") = py::none(), py::arg("k_weight") = py::none(), py::arg("norm_first") = false);
+    m.def("attention_general", &attention_general, py::arg("y"), py::arg("q_col"), py::arg("out"), py::arg("out_col"), py::arg("out_scale"),
+          py::arg("k_cache"), py::arg("v_cache"), py::arg("positions"), py::arg("token_seq"), py::arg("block_table"), py::arg("heads"),
+          py::arg("kv_heads"), py::arg("dim"), py::arg("v_dim"), py::arg("window"), py::arg("chunk"), py::arg("scale"),
+          py::arg("status") = py::none(), py::arg("keep_first") = 0, py::arg("maps") = 1, py::arg("lam") = 0.0, py::arg("sub_eps") = 0.0);
+    m.def("retention_scan", &retention_scan);
+    m.def("route_experts", &route_experts);
     m.def("silu_mul", &silu_mul, py::arg("gu"), py::arg("out"), py::arg("interleave") = 0);
     m.def("rope_store", &rope_store, py::arg("qkv"), py::arg("positions"), py::arg("cos_sin"), py::arg("k_cache"),
           py::arg("v_cache"), py::arg("token_seq"), py::arg("block_table"), py::arg("heads"), py::arg("kv_heads"),

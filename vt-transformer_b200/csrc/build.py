@@ -36,6 +36,7 @@ SOURCES = [
     "sampling.cu",
     "recurrent.cu",
     "attention_general.cu",
+    "experts.cu",
 ]
 HEADERS = ["common.cuh", "kernels.h", "launch.cuh", "tc_common.cuh", "gemm_epilogue.cuh", "attention_mma.cuh", "attention_decode.cuh", "attention_noalloc.h"]
 

@@ -80,10 +80,14 @@ cudaError_t launch_logits_scale_cap(float* logits, long long n, float scale, flo
 // depends on hidden and the block size only, never on the batch.  The delta may also come as `n_parts` 32-bit
 // shares [n_parts, n_tokens, hidden] (a matrix product whose inner dimension was cut over CTAs leaves its shares
 // unadded): they are added here in the order of their index.
+// With `post_weight` the delta is itself normed before it is added: delta * rsqrt(mean(delta^2) + post_eps) * post_weight *
+// post_mult, in 32-bit (a layer that norms a sublayer's result before the residual sum): one more pass over the delta's row
+// for its sum of squares, whose order depends on hidden and the block size only.
 template <typename T, bool Center>
 __global__ void rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta, const float* __restrict__ parts,
                                int n_parts, const float* __restrict__ weight, float eps, T* __restrict__ out,
-                               const int* __restrict__ rows, int n_tokens, int hidden, int* status) {
+                               const int* __restrict__ rows, int n_tokens, int hidden, int* status,
+                               const float* __restrict__ post_weight, float post_eps, float post_mult) {
     __shared__ float scratch[32];
     pdl_launch();
     // the norm's weight and the list of rows are written by no kernel of the step: they are read before the wait
@@ -101,10 +105,45 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delt
     const T* dr = delta ? delta + (size_t)t * hidden : nullptr;
     const float* pr = parts ? parts + (size_t)t * hidden : nullptr;
     const size_t stride = (size_t)n_tokens * hidden;
-    // v = x (+ delta, or + the shares in the order of their index) for the eight values at i
+    const int first = threadIdx.x * 8;
+    // the delta (a tensor, or the shares in the order of their index) for the eight values at i
+    auto delta_values = [&](int i, float (&d)[8]) {
+        if (dr) {
+            Vec8<T>::load(dr + i, d);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) d[j] = 0.f;
+#pragma unroll 4
+            for (int q = 0; q < n_parts; ++q) {
+                float e[8];
+                Vec8<float>::load(pr + i + q * stride, e);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) d[j] += e[j];
+            }
+        }
+    };
+    float post_rs = 0.f;
+    if (post_weight != nullptr && (dr || pr)) {
+        float ds = 0.f;
+        for (int i = first; i < hidden; i += blockDim.x * 8) {
+            float d[8];
+            delta_values(i, d);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) ds += d[j] * d[j];
+        }
+        post_rs = rsqrtf(block_sum(ds, scratch) / (float)hidden + post_eps) * post_mult;
+        __syncthreads();                                  // scratch is used again below
+    }
+    // v = x (+ delta) for the eight values at i
     auto row_values = [&](int i, float (&v)[8]) {
         Vec8<float>::load(xr + i, v);
-        if (dr) {
+        if (post_weight != nullptr && (dr || pr)) {
+            float d[8], w[8];
+            delta_values(i, d);
+            Vec8<float>::load(post_weight + i, w);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] += d[j] * post_rs * w[j];
+        } else if (dr) {
             float d[8];
             Vec8<T>::load(dr + i, d);
 #pragma unroll
@@ -119,7 +158,6 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delt
             }
         }
     };
-    const int first = threadIdx.x * 8;
     const bool once = hidden <= (int)blockDim.x * 8;      // a thread has all its values at once: they stay in registers
     float keep[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     float ss = 0.f, sm = 0.f;
@@ -176,27 +214,30 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delt
 template <bool Center>
 static cudaError_t launch_norm(int out_dtype, float* x, const void* delta, const float* parts, int n_parts,
                                const float* weight, float eps, void* out, const int* rows, int n_rows, int n_tokens,
-                               int hidden, int* status, cudaStream_t stream) {
+                               int hidden, int* status, const float* post_weight, float post_eps, float post_mult,
+                               cudaStream_t stream) {
     if (delta != nullptr && parts != nullptr) return cudaErrorInvalidValue;
     if (n_rows == 0) return cudaSuccess;
     int threads = min(512, max(32, ((hidden / 8 + 31) / 32) * 32));
     if (out_dtype == kBF16)
         return launch(rmsnorm_kernel<__nv_bfloat16, Center>, n_rows, threads, 0, stream, x, (const __nv_bfloat16*)delta, parts, n_parts, weight, eps,
-                      (__nv_bfloat16*)out, rows, n_tokens, hidden, status);
+                      (__nv_bfloat16*)out, rows, n_tokens, hidden, status, post_weight, post_eps, post_mult);
     return launch(rmsnorm_kernel<float, Center>, n_rows, threads, 0, stream, x, (const float*)delta, parts, n_parts, weight, eps, (float*)out, rows, n_tokens,
-                  hidden, status);
+                  hidden, status, post_weight, post_eps, post_mult);
 }
 
 cudaError_t launch_rmsnorm(int out_dtype, float* x, const void* delta, const float* parts, int n_parts,
                            const float* weight, float eps, void* out, const int* rows, int n_rows, int n_tokens,
-                           int hidden, int* status, cudaStream_t stream) {
-    return launch_norm<false>(out_dtype, x, delta, parts, n_parts, weight, eps, out, rows, n_rows, n_tokens, hidden, status, stream);
+                           int hidden, int* status, const float* post_weight, float post_eps, float post_mult, cudaStream_t stream) {
+    return launch_norm<false>(out_dtype, x, delta, parts, n_parts, weight, eps, out, rows, n_rows, n_tokens, hidden, status, post_weight,
+                       post_eps, post_mult, stream);
 }
 
 cudaError_t launch_layernorm(int out_dtype, float* x, const void* delta, const float* parts, int n_parts,
                              const float* weight, float eps, void* out, const int* rows, int n_rows, int n_tokens,
-                             int hidden, int* status, cudaStream_t stream) {
-    return launch_norm<true>(out_dtype, x, delta, parts, n_parts, weight, eps, out, rows, n_rows, n_tokens, hidden, status, stream);
+                             int hidden, int* status, const float* post_weight, float post_eps, float post_mult, cudaStream_t stream) {
+    return launch_norm<true>(out_dtype, x, delta, parts, n_parts, weight, eps, out, rows, n_rows, n_tokens, hidden, status, post_weight,
+                       post_eps, post_mult, stream);
 }
 
 // ------------------------------------------------------------------------- PolyNorm

@@ -51,20 +51,21 @@ struct Pool {
 
 struct Group {
     long long window;                    // keys a token sees, or -1: all
+    long long keep;                      // with a window: the first `keep` tokens stay readable, so their pages are never given back
     Pool pool;
     std::vector<int32_t> table;          // [rows, max_pages], -1 where no page is held
     std::vector<int64_t> first_live;     // [rows] first logical page that may still be held
-    Group(long long w, int pages, int rows, int max_pages)
-        : window(w), pool(pages), table((size_t)rows * max_pages, -1), first_live(rows, 0) {}
+    Group(long long w, long long keep_first, int pages, int rows, int max_pages)
+        : window(w), keep(keep_first), pool(pages), table((size_t)rows * max_pages, -1), first_live(rows, 0) {}
 };
 
 class CacheBook {
   public:
-    CacheBook(int page_size, int max_requests, long long max_seq_len, const std::vector<std::pair<long long, int>>& groups)
+    CacheBook(int page_size, int max_requests, long long max_seq_len, const std::vector<std::tuple<long long, int, long long>>& groups)
         : page_size_(page_size), rows_(max_requests), max_seq_len_(max_seq_len),
           max_pages_((int)((max_seq_len + page_size - 1) / page_size)), lengths_(max_requests, 0), live_(max_requests, 0) {
         if (page_size < 1) throw std::invalid_argument("page_size must be positive");
-        for (const auto& g : groups) groups_.emplace_back(g.first, g.second, max_requests, max_pages_);
+        for (const auto& g : groups) groups_.emplace_back(std::get<0>(g), std::get<2>(g), std::get<1>(g), max_requests, max_pages_);
         for (int r = max_requests - 1; r >= 0; --r) free_rows_.push_back(r);
     }
 
@@ -171,7 +172,8 @@ class CacheBook {
             const long long first = g.first_live[row];
             if (lo > first) {
                 int32_t* t = &g.table[(size_t)row * max_pages_];
-                for (long long i = first; i < lo && i < max_pages_; ++i)
+                const long long kept = (g.keep + page_size_ - 1) / page_size_;      // pages that hold one of the first tokens
+                for (long long i = first < kept ? kept : first; i < lo && i < max_pages_; ++i)
                     if (t[i] >= 0) {
                         g.pool.give(t[i]);
                         t[i] = -1;
@@ -457,7 +459,7 @@ PYBIND11_MODULE(VTB_HOST_MODULE_NAME, m) {
     m.def("plan_step", &plan_step, py::arg("book"), py::arg("running"), py::arg("waiting"), py::arg("max_running"),
           py::arg("max_extend_tokens"), py::arg("chunk_size"));
     py::class_<CacheBook>(m, "CacheBook")
-        .def(py::init<int, int, long long, const std::vector<std::pair<long long, int>>&>(), py::arg("page_size"),
+        .def(py::init<int, int, long long, const std::vector<std::tuple<long long, int, long long>>&>(), py::arg("page_size"),
              py::arg("max_requests"), py::arg("max_seq_len"), py::arg("groups"))
         .def_property_readonly("max_pages", &CacheBook::max_pages)
         .def_property_readonly("free_rows", &CacheBook::free_rows)

@@ -21,12 +21,12 @@ cudaError_t launch_logits_scale_cap(float* logits, long long n, float scale, flo
 // delta: parts [n_parts, n_tokens, hidden] float, the unadded shares of a delta, added in the order of their index.
 cudaError_t launch_rmsnorm(int out_dtype, float* x, const void* delta, const float* parts, int n_parts,
                            const float* weight, float eps, void* out, const int* rows, int n_rows, int n_tokens,
-                           int hidden, int* status, cudaStream_t stream);
+                           int hidden, int* status, const float* post_weight, float post_eps, float post_mult, cudaStream_t stream);
 
 // The same with the mean taken off: out[r] = weight * (v - mean(v)) * rsqrt(mean((v - mean(v))^2) + eps).
 cudaError_t launch_layernorm(int out_dtype, float* x, const void* delta, const float* parts, int n_parts,
                              const float* weight, float eps, void* out, const int* rows, int n_rows, int n_tokens,
-                             int hidden, int* status, cudaStream_t stream);
+                             int hidden, int* status, const float* post_weight, float post_eps, float post_mult, cudaStream_t stream);
 
 // out[t, :] = a N(z) + b N(z^2) + c N(z^3) + e for every row of z [n_tokens, inter], N(y) = y / sqrt(mean(y^2) + eps),
 // (a, b, c, e) = coef[0..3].  out may be z.  inter % 8 == 0; the means are over the first n_mean columns, the rest being
@@ -60,18 +60,36 @@ cudaError_t launch_head_norm_gate(int dtype, const float* o, const void* y, int 
 // The general attention (attention_general.cu).  Prepare: q [heads * dim] and k [kv_heads * dim] at their columns of y
 // are rotated (pairs (i, i + half) of each head's first 2 half dimensions, angle position * freq[i]) and, with
 // norm_eps >= 0, divided head by head by sqrt(mean(.^2) + norm_eps); q is written back, k and v [kv_heads * v_dim] go
-// into k_cache [pages, kv_heads, page_size, dim] and v_cache [.., v_dim] if store.
+// into k_cache [pages, kv_heads, page_size, dim] and v_cache [pages, v_heads, page_size, v_dim] if store.  The norm
+// multiplies by q_weight / k_weight [dim] where given, and comes before the rotation with norm_first.
 cudaError_t launch_attention_prepare(int dtype, void* y, int stride, int q_col, int k_col, int v_col, const int* positions,
                                      const int* token_seq, const float* freq, int half, float norm_eps, void* k_cache,
                                      void* v_cache, const int* block_table, int table_stride, int n_seqs, int n_pages,
                                      int n_tokens, int heads, int kv_heads, int dim, int v_dim, int page_size, int store,
-                                     int* status, cudaStream_t stream);
-// Token t at position p sees keys j <= p with j > p - window (window > 0) and j / chunk == p / chunk (chunk > 0).
+                                     int* status, int v_heads, const float* q_weight, const float* k_weight, int norm_first,
+                                     cudaStream_t stream);
+// Token t at position p sees keys j <= p with j > p - window or j < keep_first (window > 0) and j / chunk == p / chunk
+// (chunk > 0).  maps 2: q [heads, 2, dim], k_cache [pages, kv_heads * 2, page_size, dim], v_cache [pages, kv_heads, ..];
+// out = out_scale * o / sqrt(mean(o^2) + sub_eps) with o = a_1 - lam * a_2, the two maps' attentions over the same values.
 cudaError_t launch_attention_general(int dtype, const void* y, int stride, int q_col, void* out, int out_stride, int out_col,
                                      float out_scale, const void* k_cache, const void* v_cache, const int* positions,
                                      const int* token_seq, const int* block_table, int table_stride, int n_seqs, int n_pages,
                                      int n_tokens, int heads, int kv_heads, int dim, int v_dim, int page_size, int window,
-                                     int chunk, float scale, int* status, cudaStream_t stream);
+                                     int chunk, float scale, int* status, int keep_first, int maps, float lam, float sub_eps,
+                                     cudaStream_t stream);
+
+// Retention (recurrent.cu): S <- decay[h] S + (k_scale k_t) v_t^T, o_t = S^T q_t for every (sequence, head), q and k
+// rotated (pairs (i, i + half), angle positions[t] * freq[i], 32-bit) while they are staged.
+cudaError_t launch_retention_scan(int dtype, const void* y, int stride, int q_col, int k_col, int v_col, const float* decay,
+                                  float k_scale, const float* freq, int half, const int* positions, float* state, int state_rows,
+                                  const int* cu_q, const int* rows, int n_seqs, float* out, int heads, int dim, int v_dim,
+                                  int most_threads, int* status, cudaStream_t stream);
+
+// Mixture of experts (experts.cu): for each row of logits [n_tokens, experts] the `top` largest choose the experts, the
+// softmax over the chosen logits weighs them; act[t, e * inter + i] *= weight of e (0 where e was not chosen), for
+// act [n_tokens, act_stride] of `dtype`.
+cudaError_t launch_route_experts(int dtype, const float* logits, int n_tokens, int experts, int top, void* act, int act_stride,
+                                 int inter, cudaStream_t stream);
 
 // dst[t, dst_col + i] = scale * src[t, i] for src [n_tokens, n] and dst [n_tokens, dst_stride], the product in 32-bit.
 cudaError_t launch_scale_into(int dtype, const void* src, void* dst, int n_tokens, int n, int dst_stride, int dst_col, float scale,

@@ -4,6 +4,7 @@
 // The recurrences, for one head with state S [dim, v_dim] in 32-bit:
 //   gated linear attention   S <- diag(alpha_t) S + k_t v_t^T,                         o_t = S^T q_t
 //   delta rule               S <- diag(w_t) S - (a_t * u_t)(u_t^T S_old) + k_t v_t^T,  o_t = S^T r_t
+//   retention                S <- decay_h S + (k_t / sqrt(dim)) v_t^T,                  o_t = S^T q_t   (q, k rotated)
 // Column j of S depends on column j alone, so a warp owns 32 columns of one (sequence, head) and walks the step's
 // tokens of that sequence in order: a decoded token and a portion of a prompt are the same loop.  A thread keeps
 // KD rows of its column in registers; the rows are spread over `G` threads a column (G warps), whose partial dot
@@ -48,6 +49,10 @@ struct ScanArgs {
     int col_blocks;               // warps of columns in a CTA
     int most_threads;             // > 0: the step is a long walk of few sequences (CTAs of 256 threads); 0: the kernel's own bound
     int* status;
+    // retention (Fixed): bias2 holds one decay for each head, c2 scales k, and q and k are rotated while they are staged
+    const float* freq;            // [half]: pairs (i, i + half) of a head's q and k turn by positions[t] * freq[i]
+    int half;
+    const int* positions;         // [tokens]
 };
 
 __device__ __forceinline__ float log_sigmoid(float z) {
@@ -63,7 +68,9 @@ __device__ __forceinline__ float sigmoid(float z) { return 1.f / (1.f + expf(-z)
 // once), form decay, removal rate and unit key from them once for all columns, and then walk the batch's tokens out of
 // shared memory.
 // Walk: the variant for long walks of few sequences, compiled for CTAs of 256 threads (and the registers they may have).
-template <typename T, int KD, bool Delta, bool Walk>
+// Fixed: retention.  No gate: the decay is one number a head, k (not q) carries the scale, and the staged q and k are
+// rotated in 32-bit where they lie in shared memory.
+template <typename T, int KD, bool Delta, bool Walk, bool Fixed>
 __global__ void __launch_bounds__(Walk ? 256 : scan_threads(KD), 1)
 scan_kernel(const ScanArgs a) {
     extern __shared__ __align__(16) float smem[];
@@ -110,7 +117,7 @@ scan_kernel(const ScanArgs a) {
             if (i >= dim) return 0.f;
             const int col = which == 0 ? a.q_col : (which == 1 ? a.k_col : a.a_col);
             const float v = to_float(yr[col + h * dim + i]);
-            return (!Delta && which == 0) ? v * a.c2 : v;
+            return (!Delta && which == (Fixed ? 1 : 0)) ? v * a.c2 : v;
         }
         r -= kVectors * dim_p;
         if (r < rank) {
@@ -147,7 +154,7 @@ scan_kernel(const ScanArgs a) {
             to_at[k] = (int)((which == 0 ? qs : (which == 1 ? ks : bs)) - smem) + i;
             to_step[k] = dim_p;
             if (i < dim) from_col[k] = (which == 0 ? a.q_col : (which == 1 ? a.k_col : a.a_col)) + h * dim + i;
-            if (!Delta && which == 0) times[k] = a.c2;
+            if (!Delta && which == (Fixed ? 1 : 0)) times[k] = a.c2;
             continue;
         }
         r -= kVectors * dim_p;
@@ -199,7 +206,26 @@ scan_kernel(const ScanArgs a) {
             for (int r = tid + kScanValues * n_threads; r < per; r += n_threads) place(tb, r, fetch(yr, r));
         }
         __syncthreads();
-        for (int e = tid; e < n * dim_p; e += n_threads) {
+        if (Fixed) {
+            const float decay = a.bias2[h];
+            for (int e = tid; e < n * dim_p; e += n_threads) ds[e] = (e % dim_p) < dim ? decay : 0.f;
+            // the rotation of q and k: a thread turns both members of a pair, so nothing else touches them meanwhile
+            const int half = a.half;
+            for (int e = tid; e < n * half; e += n_threads) {
+                const int tb = e / half, i = e % half;
+                const float angle = (float)a.positions[tb0 + tb] * a.freq[i];
+                float sn, cs;
+                sincosf(angle, &sn, &cs);
+                float* qv = qs + tb * dim_p;
+                float* kv = ks + tb * dim_p;
+                const float qa = qv[i], qb = qv[i + half], ka = kv[i], kb = kv[i + half];
+                qv[i] = qa * cs - qb * sn;
+                qv[i + half] = qb * cs + qa * sn;
+                kv[i] = ka * cs - kb * sn;
+                kv[i + half] = kb * cs + ka * sn;
+            }
+        }
+        for (int e = tid; !Fixed && e < n * dim_p; e += n_threads) {
             const int tb = e / dim_p, i = e % dim_p;
             float d = 0.f;
             if (i < dim) {
@@ -307,7 +333,7 @@ scan_kernel(const ScanArgs a) {
     }
 }
 
-template <typename T, int KD, bool Delta, bool Walk>
+template <typename T, int KD, bool Delta, bool Walk, bool Fixed>
 cudaError_t launch_scan_kd(ScanArgs a, int n_seqs, cudaStream_t stream) {
     static std::atomic<unsigned long long> done{0};
     const int G = a.groups, dim_p = G * KD;
@@ -326,13 +352,13 @@ cudaError_t launch_scan_kd(ScanArgs a, int n_seqs, cudaStream_t stream) {
     constexpr int kMostBytes = 200 * 1024;
     if (bytes > kMostBytes) return cudaErrorInvalidValue;
     // the limit is set once for each device, so it is the most any launch may ask for, not what this one asks for
-    cudaError_t e = allow_dynamic_smem(scan_kernel<T, KD, Delta, Walk>, kMostBytes, done);
+    cudaError_t e = allow_dynamic_smem(scan_kernel<T, KD, Delta, Walk, Fixed>, kMostBytes, done);
     if (e != cudaSuccess) return e;
     dim3 grid(n_seqs, a.heads, (col_warps + a.col_blocks - 1) / a.col_blocks), block(kScanCols, G, a.col_blocks);
-    return launch(scan_kernel<T, KD, Delta, Walk>, grid, block, bytes, stream, a);
+    return launch(scan_kernel<T, KD, Delta, Walk, Fixed>, grid, block, bytes, stream, a);
 }
 
-template <typename T, bool Delta>
+template <typename T, bool Delta, bool Fixed = false>
 cudaError_t launch_scan_t(ScanArgs a, int n_seqs, cudaStream_t stream) {
     // Rows a thread: 16 where that makes at most 8 groups of warps a column, else 32, 64, 128.  Few rows a thread make
     // the walk along the tokens short (a token costs a thread rows / 4 steps of loads and multiply-adds, whatever the
@@ -341,10 +367,10 @@ cudaError_t launch_scan_t(ScanArgs a, int n_seqs, cudaStream_t stream) {
     a.groups = (a.dim + kd - 1) / kd;
     if (a.groups > 8) return cudaErrorInvalidValue;
     const bool walk = a.most_threads > 0;
-    if (kd == 16) return walk ? launch_scan_kd<T, 16, Delta, true>(a, n_seqs, stream) : launch_scan_kd<T, 16, Delta, false>(a, n_seqs, stream);
-    if (kd == 32) return walk ? launch_scan_kd<T, 32, Delta, true>(a, n_seqs, stream) : launch_scan_kd<T, 32, Delta, false>(a, n_seqs, stream);
-    if (kd == 64) return walk ? launch_scan_kd<T, 64, Delta, true>(a, n_seqs, stream) : launch_scan_kd<T, 64, Delta, false>(a, n_seqs, stream);
-    return launch_scan_kd<T, 128, Delta, false>(a, n_seqs, stream);
+    if (kd == 16) return walk ? launch_scan_kd<T, 16, Delta, true, Fixed>(a, n_seqs, stream) : launch_scan_kd<T, 16, Delta, false, Fixed>(a, n_seqs, stream);
+    if (kd == 32) return walk ? launch_scan_kd<T, 32, Delta, true, Fixed>(a, n_seqs, stream) : launch_scan_kd<T, 32, Delta, false, Fixed>(a, n_seqs, stream);
+    if (kd == 64) return walk ? launch_scan_kd<T, 64, Delta, true, Fixed>(a, n_seqs, stream) : launch_scan_kd<T, 64, Delta, false, Fixed>(a, n_seqs, stream);
+    return launch_scan_kd<T, 128, Delta, false, Fixed>(a, n_seqs, stream);
 }
 
 }  // namespace
@@ -367,6 +393,19 @@ cudaError_t launch_delta_scan(int dtype, const void* y, int stride, int r_col, i
     ScanArgs a = {y, stride, r_col, k_col, v_col, a_col, low_col, rank, w2, w0, a_bias, decay_rate, key_eps, state,
                   state_rows, cu_q, rows, out, heads, dim, dim, 1, 1, most_threads, status};
     return dtype == kBF16 ? launch_scan_t<__nv_bfloat16, true>(a, n_seqs, stream) : launch_scan_t<float, true>(a, n_seqs, stream);
+}
+
+cudaError_t launch_retention_scan(int dtype, const void* y, int stride, int q_col, int k_col, int v_col, const float* decay,
+                                  float k_scale, const float* freq, int half, const int* positions, float* state, int state_rows,
+                                  const int* cu_q, const int* rows, int n_seqs, float* out, int heads, int dim, int v_dim,
+                                  int most_threads, int* status, cudaStream_t stream) {
+    if (n_seqs == 0) return cudaSuccess;
+    if (2 * half > dim) return cudaErrorInvalidValue;
+    // no low-rank gate (rank 0); the gate's bias slot carries the heads' decays, c2 the scale of k
+    ScanArgs a = {y, stride, q_col, k_col, v_col, 0, 0, 0, nullptr, decay, nullptr, 0.f, k_scale, state, state_rows, cu_q, rows,
+                  out, heads, dim, v_dim, 1, 1, most_threads, status, freq, half, positions};
+    return dtype == kBF16 ? launch_scan_t<__nv_bfloat16, false, true>(a, n_seqs, stream)
+                          : launch_scan_t<float, false, true>(a, n_seqs, stream);
 }
 
 // ------------------------------------------------------------------------- norm of each head's output, gate

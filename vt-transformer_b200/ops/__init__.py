@@ -85,23 +85,36 @@ def dense(t, dtype=None) -> torch.Tensor:
     return t if dtype is None else t.to(dtype)
 
 
+def _post(post):
+    """(weight, eps, mult) of a delta that is normed before it is added, as the kernels' last three arguments."""
+    if post is None:
+        return ()
+    weight, eps, mult = post
+    return (weight, float(eps), float(mult))
+
+
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, delta=None,
-            rows: Optional[torch.Tensor] = None, status=None) -> torch.Tensor:
+            rows: Optional[torch.Tensor] = None, status=None, post=None) -> torch.Tensor:
     """out = weight * v * rsqrt(mean(v^2) + eps) over the rows ``rows`` (all) of v = x + delta, which is
-    written back to x.  ``delta``: None, a tensor of out's dtype, or a ``SplitSum``."""
+    written back to x.  ``delta``: None, a tensor of out's dtype, or a ``SplitSum``.  With ``post`` = (w [H] float32,
+    e, m) the delta is normed and scaled first, all in 32-bit: v = x + m * w * delta * rsqrt(mean(delta^2) + e)."""
     if isinstance(delta, SplitSum):
         delta = delta.shares
-    backend().rmsnorm(x, delta, weight, float(eps), out, rows, status)
+    if post is not None and delta is None:
+        raise ValueError("rmsnorm: a delta to norm before it is added was announced and none came")
+    backend().rmsnorm(x, delta, weight, float(eps), out, rows, status, *_post(post))
     return out
 
 
 def layernorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, delta=None,
-              rows: Optional[torch.Tensor] = None, status=None) -> torch.Tensor:
+              rows: Optional[torch.Tensor] = None, status=None, post=None) -> torch.Tensor:
     """out = weight * (v - mean(v)) * rsqrt(var(v) + eps) over the rows ``rows`` (all) of v = x + delta, which is
-    written back to x; var is the mean of the squared deviations.  ``delta`` as for ``rmsnorm``."""
+    written back to x; var is the mean of the squared deviations.  ``delta`` and ``post`` as for ``rmsnorm``."""
     if isinstance(delta, SplitSum):
         delta = delta.shares
-    backend().layernorm(x, delta, weight, float(eps), out, rows, status)
+    if post is not None and delta is None:
+        raise ValueError("layernorm: a delta to norm before it is added was announced and none came")
+    backend().layernorm(x, delta, weight, float(eps), out, rows, status, *_post(post))
     return out
 
 
@@ -164,27 +177,58 @@ def delta_scan(y, r_col: int, k_col: int, v_col: int, a_col: int, w1_col: int, w
     return o
 
 
+def retention_scan(y, q_col: int, k_col: int, v_col: int, decay: torch.Tensor, k_scale: float, frequencies, state: torch.Tensor,
+                   ctx, o: torch.Tensor, heads: int, dim: int, v_dim: int, status=None):
+    """Retention over the step's tokens, sequence by sequence and head by head, in the order of the tokens:
+    S <- decay[h] S + (k_scale * k_t) v_t^T, o_t = S^T q_t, after the first 2 * len(frequencies) dimensions of every
+    head of q and k were rotated, pairs (i, i + len), by position * frequencies[i] (a 32-bit product, in 32-bit;
+    ``frequencies`` None: no rotation).  q, k and v are columns of ``y``; ``decay`` [heads] float32; ``state``
+    [request rows, heads, dim, v_dim] (float32) is read at the step's ``ctx.rows`` and left as after the last token;
+    ``o`` [T, heads * v_dim] is float32.  Rotation, state and sums are 32-bit."""
+    backend().retention_scan(y, int(q_col), int(k_col), int(v_col), decay, float(k_scale), frequencies, ctx.positions, state,
+                             ctx.cu_q, ctx.rows, o, int(heads), int(dim), int(v_dim), status, _scan_threads(ctx))
+    return o
+
+
 def attention_prepare(y, q_col: int, k_col: int, v_col: int, ctx, frequencies, norm_eps, k_cache, v_cache, block_table,
-                      heads: int, kv_heads: int, dim: int, v_dim: int, store: bool = True, status=None) -> None:
+                      heads: int, kv_heads: int, dim: int, v_dim: int, store: bool = True, status=None, v_heads=None,
+                      q_weight=None, k_weight=None, norm_first: bool = False) -> None:
     """What the general attention does to a step's q, k and v (columns of ``y``) before its keys are walked: the
     first 2 * len(frequencies) dimensions of every head of q and k are rotated, pairs (i, i + len), by
-    position * frequencies[i] (a 32-bit product; ``frequencies`` None: no rotation); then, with ``norm_eps`` not None,
-    every head of q and k is divided by sqrt(mean(.^2) + norm_eps); q is written back into ``y``, k and v go into
-    their pages ([pages, kv_heads, page_size, dim] and [..., v_dim]) if ``store``."""
+    position * frequencies[i] (a 32-bit product; ``frequencies`` None: no rotation); with ``norm_eps`` not None,
+    every head of q and k is divided by sqrt(mean(.^2) + norm_eps) and multiplied by ``q_weight`` / ``k_weight``
+    ([dim] float32, or None), after the rotation or, with ``norm_first``, before it; q is written back into ``y``, k and
+    v go into their pages ([pages, kv_heads, page_size, dim] and [pages, v_heads, page_size, v_dim]; ``v_heads``
+    None: as many as kv_heads) if ``store``."""
     backend().attention_prepare(y, int(q_col), int(k_col), int(v_col), ctx.positions, ctx.token_seq, frequencies,
                                 -1.0 if norm_eps is None else float(norm_eps), k_cache, v_cache, block_table, int(heads),
-                                int(kv_heads), int(dim), int(v_dim), bool(store), status)
+                                int(kv_heads), int(dim), int(v_dim), bool(store), status,
+                                int(kv_heads if v_heads is None else v_heads), q_weight, k_weight, bool(norm_first))
 
 
 def attention_general(y, q_col: int, out, out_col: int, out_scale: float, k_cache, v_cache, ctx, block_table, heads: int,
-                      kv_heads: int, dim: int, v_dim: int, window, chunk, scale: float, status=None):
+                      kv_heads: int, dim: int, v_dim: int, window, chunk, scale: float, status=None, keep_first: int = 0,
+                      maps: int = 1, lam: float = 0.0, sub_eps: float = 0.0):
     """out[t, out_col + h * v_dim + :] = out_scale * softmax(scale * q . k_j) v_j over the keys j that token t at
-    position p sees: j <= p, j > p - window (if a window is given) and j // chunk == p // chunk (if chunks are).
-    q is read at column ``q_col`` of ``y``; keys of size ``dim`` and values of size ``v_dim`` from their pages."""
+    position p sees: j <= p, and j > p - window or j < keep_first (if a window is given), and j // chunk == p // chunk
+    (if chunks are).  q is read at column ``q_col`` of ``y``; keys of size ``dim`` and values of size ``v_dim`` from
+    their pages.  ``maps`` 2: every head has two queries [2, dim] and every head of values two heads of keys (k pages
+    [pages, kv_heads * 2, page_size, dim]); with a_1 and a_2 the two attentions over the same values,
+    o = a_1 - lam * a_2 and out = out_scale * o / sqrt(mean(o^2) + sub_eps), all in 32-bit."""
     backend().attention_general(y, int(q_col), out, int(out_col), float(out_scale), k_cache, v_cache, ctx.positions,
                                 ctx.token_seq, block_table, int(heads), int(kv_heads), int(dim), int(v_dim),
-                                int(window) if window else 0, int(chunk) if chunk else 0, float(scale), status)
+                                int(window) if window else 0, int(chunk) if chunk else 0, float(scale), status,
+                                int(keep_first), int(maps), float(lam), float(sub_eps))
     return out
+
+
+def route_experts(logits: torch.Tensor, top: int, act: torch.Tensor, inter: int) -> torch.Tensor:
+    """For every token (row): the ``top`` largest of its router logits [experts] (float32; the lower index among
+    equals) choose its experts, the softmax over the chosen logits weighs them; columns [e * inter, (e + 1) * inter) of
+    ``act`` (what expert e's last product multiplies) are multiplied by expert e's weight, and set to zero for an
+    expert that was not chosen.  Columns beyond experts * inter (an expert that every token uses) stay."""
+    backend().route_experts(logits, int(top), act, int(inter))
+    return act
 
 
 def scale_into(src: torch.Tensor, dst: torch.Tensor, dst_col: int, scale: float) -> torch.Tensor:
@@ -622,6 +666,6 @@ def _counted(fn):
     return wrapper
 
 
-for _name in ("embedding", "logits_scale_cap", "rmsnorm", "layernorm", "polynorm", "scale_into", "head_norm_gate", "gla_scan", "delta_scan",
+for _name in ("embedding", "logits_scale_cap", "rmsnorm", "layernorm", "polynorm", "scale_into", "head_norm_gate", "gla_scan", "delta_scan", "retention_scan", "route_experts",
               "attention_prepare", "attention_general", "silu_mul", "rope_store", "linear", "paged_attention", "argmax", "sample"):  # the others count where they launch
     globals()[_name] = _counted(globals()[_name])

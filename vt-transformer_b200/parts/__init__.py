@@ -3,6 +3,7 @@ from . import attention, block, embedding, linear_attention, mlp, norm, projecte
 from .base import (Block, CacheView, Embedding, FeedForward, Head, KVCacheSpec, Mixer, Norm, ParamSpec, Part, PositionEncoding,
                    ResidualStream, Runtime, StateLayout, StateSpec, PagedLayout, build_part, register_cache_kind, register_part,
                    unregister_cache_kind, unregister_part)
-from .specs import (AttentionSpec, BlockSpec, DeltaRuleSpec, EmbeddingSpec, FeedForwardSpec, GatedLinearAttentionSpec, GatedMLPSpec,
+from .specs import (AttentionSpec, BlockSpec, DeltaRuleSpec, DifferentialAttentionSpec, EmbeddingSpec, ExpertsSpec, FeedForwardSpec,
+                    GatedLinearAttentionSpec, GatedMLPSpec, RetentionSpec,
                     HeadSpec, MixerSpec, ModelSpec, NormSpec, ParallelSpec, PolyNormMLPSpec, PositionSpec, RunSpec)
 from .projected import ProjectedMixer

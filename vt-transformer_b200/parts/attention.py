@@ -13,7 +13,7 @@ def _attention(spec, prefix, rt):
     """The attention mixer for a spec: the kernels of ``PagedAttention`` take the whole head rotated from a table,
     values as wide as keys and a causal or windowed mask; everything else runs ``GeneralAttention``."""
     plain = (spec.v_dim in (None, spec.head_dim) and spec.qk_norm_eps is None and spec.chunk is None
-             and spec.position.kind != "rotary_computed")
+             and spec.position.kind != "rotary_computed" and not spec.keep_first)
     return (PagedAttention if plain else GeneralAttention)(spec, prefix, rt)
 
 
@@ -125,7 +125,8 @@ class GeneralAttention(ProjectedMixer):
 
     def cache_spec(self):
         s = self.spec
-        return KVCacheSpec(s.kv_heads, s.head_dim, s.window, v_dim=self.v_dim if self.v_dim != s.head_dim else None)
+        return KVCacheSpec(s.kv_heads, s.head_dim, s.window, v_dim=self.v_dim if self.v_dim != s.head_dim else None,
+                           keep_first=s.keep_first if s.window else 0)
 
     def param_specs(self):
         s, p, x = self.spec, self.prefix, self.spec.weight_suffix
@@ -163,7 +164,7 @@ class GeneralAttention(ProjectedMixer):
         k_pages, v_pages = cache.pages["k"], cache.pages["v"]
         ops.attention_prepare(y, cols[0], cols[1], cols[2], ctx, freq, s.qk_norm_eps, k_pages, v_pages, cache.block_table,
                               s.heads, s.kv_heads, s.head_dim, self.v_dim, store=cache.writes, status=ctx.status)
-        if cols[0] == 0 and ops.tensor_core_attention_takes(y.dtype, s.heads, s.kv_heads, s.head_dim, self.v_dim, cache.page_size):
+        if cols[0] == 0 and not s.keep_first and ops.tensor_core_attention_takes(y.dtype, s.heads, s.kv_heads, s.head_dim, self.v_dim, cache.page_size):
             # values as wide as keys at a head size the tensor-core kernels take: the kernels of the plain attention walk
             # the keys (tcgen05 for long portions, mma.sync tiles, the single-token kernel), with the chunks as one more
             # bound of the keys a row sees.  They write a tensor of their own, which is then scaled into its columns.
@@ -176,4 +177,85 @@ class GeneralAttention(ProjectedMixer):
                 ops.scale_into(o, out, out_col, out_scale)
             return
         ops.attention_general(y, cols[0], out, out_col, out_scale, k_pages, v_pages, ctx, cache.block_table, s.heads,
-                              s.kv_heads, s.head_dim, self.v_dim, s.window, s.chunk, self.scale, status=ctx.status)
+                              s.kv_heads, s.head_dim, self.v_dim, s.window, s.chunk, self.scale, status=ctx.status,
+                              keep_first=s.keep_first if s.window else 0)
+
+
+@register_part("mixer", "differential_attention")
+class DifferentialAttention(ProjectedMixer):
+    """See ``DifferentialAttentionSpec``.  q, k and v are one product.  One kernel norms q and k map by map (32-bit,
+    weights), rotates them and stores k and v into the pages: the two maps of a head of values are two heads of keys
+    ([pages, kv_heads * 2, page, head_dim]) beside one head of values.  The attention kernel walks a token's visible
+    keys once for both maps (the first tokens that stay visible, then the window), each with a running maximum and sum
+    of its own over the same values, and ends with the difference, its norm and the factor 1 - diff.  lam is one
+    number a layer, formed in 32-bit when the weights are loaded."""
+
+    def __init__(self, spec, prefix, rt):
+        super().__init__(spec, prefix, rt)
+        if spec.heads % spec.kv_heads:
+            raise ValueError(f"differential attention: {spec.heads} heads over {spec.kv_heads} key/value heads")
+        if spec.position.kind not in ("rotary_computed", "none"):
+            raise ValueError(f"differential attention: position encoding '{spec.position.kind}' is not built; known: "
+                             f"rotary_computed, none")
+        if spec.position.kind != "none" and (spec.position.dim % 2 or spec.position.dim > spec.head_dim):
+            raise ValueError(f"differential attention: the rotation covers {spec.position.dim} dimensions; it must be even "
+                             f"and at most the head's {spec.head_dim}")
+        self.position = build_part("position", spec.position, prefix, rt)
+        self.scale = spec.scale if spec.scale is not None else 1.0 / math.sqrt(spec.head_dim)
+        self.keep_first = spec.keep_first if spec.window else 0
+
+    def cache_spec(self):
+        s = self.spec
+        return KVCacheSpec(s.kv_heads, s.head_dim, s.window, v_dim=s.v_dim if s.v_dim != s.head_dim else None, k_maps=2,
+                           keep_first=self.keep_first)
+
+    def param_specs(self):
+        s, p = self.spec, self.prefix
+        q, k, v, o, qn, kn, lq1, lk1, lq2, lk2 = s.names
+        out = {
+            p + q: ParamSpec((s.heads * 2 * s.head_dim, s.hidden)), p + k: ParamSpec((s.kv_heads * 2 * s.head_dim, s.hidden)),
+            p + v: ParamSpec((s.kv_heads * s.v_dim, s.hidden)), p + o: ParamSpec((s.hidden, s.heads * s.v_dim)),
+            p + qn: ParamSpec((s.head_dim,), role="vector", init="one_plus_normal"),
+            p + kn: ParamSpec((s.head_dim,), role="vector", init="one_plus_normal"),
+        }
+        out.update({p + n: ParamSpec((s.head_dim,), role="vector") for n in (lq1, lk1, lq2, lk2)})
+        return out
+
+    def load(self, get) -> None:
+        s, p, rt = self.spec, self.prefix, self.rt
+        q, k, v, o, qn, kn, lq1, lk1, lq2, lk2 = s.names
+        self._in = [rt.param(get(p + n)) for n in (q, k, v)]
+        self.w_o = rt.param(get(p + o))
+        self.q_weight = rt.param(get(p + qn), "vector")
+        self.k_weight = rt.param(get(p + kn), "vector")
+        l1 = float((rt.param(get(p + lq1), "vector").double() * rt.param(get(p + lk1), "vector").double()).sum())
+        l2 = float((rt.param(get(p + lq2), "vector").double() * rt.param(get(p + lk2), "vector").double()).sum())
+        self.lam = math.exp(l1) - math.exp(l2) + s.diff           # one number a layer, formed once
+        self.position.load(get)
+        self.pack()
+
+    def release_unpacked(self) -> None:
+        self._in = self.w_o = None
+
+    def in_matrices(self):
+        return list(self._in)
+
+    def out_matrix(self):
+        return self.w_o
+
+    def inner_size(self) -> int:
+        return self.spec.heads * self.spec.v_dim
+
+    def extra_weight_bytes(self) -> int:
+        return 4 * (self.q_weight.numel() + self.k_weight.numel())
+
+    def core(self, y, cols, ctx, cache, out, out_col, out_scale) -> None:
+        s, ops = self.spec, self.rt.ops
+        freq = getattr(self.position, "frequencies", None)
+        k_pages, v_pages = cache.pages["k"], cache.pages["v"]
+        ops.attention_prepare(y, cols[0], cols[1], cols[2], ctx, freq, s.norm_eps, k_pages, v_pages, cache.block_table,
+                              s.heads * 2, s.kv_heads * 2, s.head_dim, s.v_dim, store=cache.writes, status=ctx.status,
+                              v_heads=s.kv_heads, q_weight=self.q_weight, k_weight=self.k_weight, norm_first=True)
+        ops.attention_general(y, cols[0], out, out_col, out_scale * (1.0 - s.diff), k_pages, v_pages, ctx, cache.block_table,
+                              s.heads, s.kv_heads, s.head_dim, s.v_dim, s.window, None, self.scale, status=ctx.status,
+                              keep_first=self.keep_first, maps=2, lam=self.lam, sub_eps=s.norm_eps)

@@ -107,6 +107,8 @@ class KVCacheSpec:
     head_dim: int
     window: Optional[int] = None
     v_dim: Optional[int] = None        # size of a value where it differs from a key's (None: head_dim)
+    k_maps: int = 1                    # keys a token has for each head of values (kv_heads * k_maps heads of keys)
+    keep_first: int = 0                # with a window: the tokens at positions below this stay readable
 
 
 @dataclass(frozen=True)
@@ -121,9 +123,11 @@ class PagedLayout:
     """What a kind of cache spec keeps for every token, in pages.  ``tensors``: (name, outer, inner) for each
     tensor; the pool's tensor of that name is [pages, outer, page_size, inner] for a slot (keys: outer = KV heads,
     inner = head size, so that a (page, head) run of keys is contiguous).  ``window`` None keeps all tokens, w
-    the last w: pages that the window has passed go back to the pool."""
+    the last w: pages that the window has passed go back to the pool, except those that hold one of the first
+    ``keep_first`` tokens."""
     tensors: Tuple[Tuple[str, int, int], ...]
     window: Optional[int] = None
+    keep_first: int = 0
 
 
 @dataclass(frozen=True)
@@ -154,8 +158,9 @@ def cache_layout(spec):
                     f"(parts.register_cache_kind adds one)")
 
 
-register_cache_kind(KVCacheSpec, lambda s: PagedLayout((("k", s.kv_heads, s.head_dim),
-                                                        ("v", s.kv_heads, s.v_dim if s.v_dim else s.head_dim)), s.window))
+register_cache_kind(KVCacheSpec, lambda s: PagedLayout((("k", s.kv_heads * s.k_maps, s.head_dim),
+                                                        ("v", s.kv_heads, s.v_dim if s.v_dim else s.head_dim)), s.window,
+                                                       s.keep_first if s.window is not None else 0))
 register_cache_kind(StateSpec, lambda s: StateLayout(tuple(s.shape), s.dtype))
 
 
@@ -221,11 +226,20 @@ class Norm(Part):
     Returns the normed rows in the compute dtype.
 
     A norm whose kernel can add the unadded 32-bit shares of a matrix product itself sets ``takes_shares``; it is
-    then given what ``ops.linear_to_stream`` returned as it is.  Any other norm gets an ordinary tensor."""
+    then given what ``ops.linear_to_stream`` returned as it is.  Any other norm gets an ordinary tensor.
+
+    ``post`` = (weight [H] float32, eps, mult): the delta is itself normed before it is added,
+    x + mult * weight * delta / sqrt(mean(delta^2) + eps), all in 32-bit (a layer that norms a sublayer's result
+    before the residual sum).  A norm whose kernel does that sets ``takes_post``; ``weighted()`` is the weight as the
+    kernel multiplies with it."""
     category = "norm"
     takes_shares = False
+    takes_post = False
 
-    def __call__(self, x, delta=None, rows=None, status=None):
+    def __call__(self, x, delta=None, rows=None, status=None, post=None):
+        raise NotImplementedError
+
+    def weighted(self):
         raise NotImplementedError
 
 
@@ -306,17 +320,24 @@ class ResidualStream:
         self.x = x
         self.status = status
         self.pending: Optional[torch.Tensor] = None
+        self.pending_post = None
 
     def normed(self, norm: Norm, rows=None):
         delta, self.pending = self.pending, None
+        post, self.pending_post = self.pending_post, None
         if delta is not None and not isinstance(delta, torch.Tensor) and not getattr(norm, "takes_shares", False):
             delta = norm.rt.ops.dense(delta, norm.rt.dtype)       # unadded shares, for a norm that wants a tensor
-        return norm(self.x, delta=delta, rows=rows, status=self.status)
+        if post is None:
+            return norm(self.x, delta=delta, rows=rows, status=self.status)
+        if not getattr(norm, "takes_post", False):
+            raise RuntimeError(f"norm '{norm.spec.kind}' cannot add a delta that is normed first")
+        return norm(self.x, delta=delta, rows=rows, status=self.status, post=post)
 
-    def add(self, delta) -> None:
+    def add(self, delta, post=None) -> None:
+        """``post`` = (weight, eps, mult): the delta is normed and scaled before it is added (see ``Norm``)."""
         if self.pending is not None:
             raise RuntimeError("the residual stream holds a delta that no norm has added yet")
-        self.pending = delta
+        self.pending, self.pending_post = delta, post
 
 
 # ----------------------------------------------------------------------------- registry

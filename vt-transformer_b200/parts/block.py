@@ -57,3 +57,30 @@ class PreNormBlock(Block):
             return
         h = stream.normed(self.norm2)
         stream.add(self.ffn.forward(h, ctx))
+
+
+@register_part("block", "sandwich")
+class SandwichBlock(PreNormBlock):
+    """x += m * post1(mixer(norm1(x))); x += m * post2(ffn(norm2(x))): every sublayer's result is normed (root mean
+    square, weight) and multiplied by m before the residual sum.  The norm that reads the stream next does all of it
+    in one pass: it norms and scales the pending result in 32-bit, adds it, and norms the sum."""
+
+    def __init__(self, spec, prefix, rt):
+        super().__init__(spec, prefix, rt)
+        if spec.post1 is None or (spec.ffn is not None and spec.post2 is None):
+            raise ValueError("sandwich block: a norm for each sublayer's result (post1, post2)")
+        for n in (spec.post1, spec.post2):
+            if n is not None and n.kind != "rmsnorm":
+                raise ValueError(f"sandwich block: the norm of a sublayer's result is a root-mean-square norm, not '{n.kind}'")
+        self.post1 = build_part("norm", spec.post1, prefix + spec.post1_name, rt)
+        self.post2 = build_part("norm", spec.post2, prefix + spec.post2_name, rt) if spec.ffn is not None else None
+        self.parts = self.parts + tuple(p for p in (self.post1, self.post2) if p is not None)
+
+    def forward(self, stream, ctx, cache):
+        s = self.spec
+        h = stream.normed(self.norm1)
+        stream.add(self.mixer.forward(h, ctx, cache), post=(self.post1.weighted(), s.post1.eps, s.residual_mult))
+        if self.ffn is None:
+            return
+        h = stream.normed(self.norm2)
+        stream.add(self.ffn.forward(h, ctx), post=(self.post2.weighted(), s.post2.eps, s.residual_mult))

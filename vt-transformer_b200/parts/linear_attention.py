@@ -6,7 +6,7 @@ from __future__ import annotations
 
 import torch
 
-from .base import ParamSpec, StateSpec, register_part
+from .base import ParamSpec, StateSpec, build_part, register_part
 from .projected import ProjectedMixer
 
 
@@ -117,4 +117,55 @@ class DeltaRule(_Recurrent):
         ops.delta_scan(y, cols[0], cols[1], cols[2], cols[4], cols[5], self.w2, self.w0, self.a_bias, s.decay_rate,
                        s.key_eps, cache.state, ctx, o, s.heads, s.dim, status=ctx.status)
         ops.head_norm_gate(o, y, cols[3], self.norm, True, s.norm_eps, "sigmoid", out, out_col, out_scale, s.heads, s.dim,
+                           token_seq=ctx.token_seq)
+
+
+@register_part("mixer", "retention")
+class Retention(_Recurrent):
+    """See ``RetentionSpec``.  Projections q, k, v and gate are one product; the scan kernel rotates q and k in 32-bit
+    while it stages them, scales k and walks the tokens with the head's decay; a second kernel norms each head's
+    output (no weight) and gates it."""
+
+    def __init__(self, spec, prefix, rt):
+        super().__init__(spec, prefix, rt)
+        if len(spec.decay) != spec.heads:
+            raise ValueError(f"retention: {len(spec.decay)} decays for {spec.heads} heads")
+        if spec.position.kind not in ("rotary_computed", "none"):
+            raise ValueError(f"retention: position encoding '{spec.position.kind}' is not built; known: rotary_computed, none")
+        if spec.position.kind != "none" and (spec.position.dim % 2 or spec.position.dim > spec.dim):
+            raise ValueError(f"retention: the rotation covers {spec.position.dim} dimensions; it must be even and at most "
+                             f"the head's {spec.dim}")
+        self.position = build_part("position", spec.position, prefix, rt)
+
+    def cache_spec(self):
+        s = self.spec
+        return StateSpec((s.heads, s.dim, s.v_dim), torch.float32)
+
+    def param_specs(self):
+        s, p = self.spec, self.prefix
+        q, k, v, g, o = s.names
+        hd, hv = s.heads * s.dim, s.heads * s.v_dim
+        return {p + q: ParamSpec((hd, s.hidden)), p + k: ParamSpec((hd, s.hidden)), p + v: ParamSpec((hv, s.hidden)),
+                p + g: ParamSpec((hv, s.hidden)), p + o: ParamSpec((s.hidden, hv))}
+
+    def load(self, get) -> None:
+        s, p, rt = self.spec, self.prefix, self.rt
+        q, k, v, g, o = s.names
+        self._in = [rt.param(get(p + n)) for n in (q, k, v, g)]
+        self.w_o = rt.param(get(p + o))
+        self.decay = torch.tensor(list(s.decay), dtype=torch.float64).to(torch.float32).to(rt.device)
+        self.ones = torch.ones(s.v_dim, dtype=torch.float32, device=rt.device)      # the heads' norm has no weight
+        self._small = (self.decay,)
+        self.position.load(get)
+        self.pack()
+
+    def inner_size(self) -> int:
+        return self.spec.heads * self.spec.v_dim
+
+    def core(self, y, cols, ctx, cache, out, out_col, out_scale) -> None:
+        s, ops = self.spec, self.rt.ops
+        o = torch.empty((y.shape[0], s.heads * s.v_dim), dtype=torch.float32, device=y.device)
+        ops.retention_scan(y, cols[0], cols[1], cols[2], self.decay, s.dim ** -0.5, getattr(self.position, "frequencies", None),
+                           cache.state, ctx, o, s.heads, s.dim, s.v_dim, status=ctx.status)
+        ops.head_norm_gate(o, y, cols[3], self.ones, False, s.norm_eps, "silu", out, out_col, out_scale, s.heads, s.v_dim,
                            token_seq=ctx.token_seq)

@@ -1,4 +1,4 @@
-"""Dense feed-forwards: gated, and with the PolyNorm activation."""
+"""Feed-forwards: gated, with the PolyNorm activation, and a mixture of gated experts."""
 from __future__ import annotations
 
 import torch
@@ -91,3 +91,71 @@ class PolyNormMLP(FeedForward):
         ops.linear(h, self.w_up, None, z, then=ops.product_hint(self.w_down, "stream"))
         ops.polynorm(z, self.coefficients, s.eps, z, n_mean=s.inter)
         return ops.linear_to_stream(z, self.w_down, None, then=self.then)
+
+
+@register_part("feed_forward", "experts")
+class Experts(FeedForward):
+    """See ``ExpertsSpec``.  The router's logits are a 32-bit product (its matrix is kept in 32-bit).  All experts'
+    gate and up matrices, and the shared expert's, are one packed matrix, so silu(gate) * up of every expert for every
+    token is ONE product with the activation in its epilogue; one kernel then picks each token's experts, forms their
+    weights and multiplies the chosen experts' columns by them (zero for the others); the down matrices are packed
+    along the inner dimension, so the weighted sum over the experts and the shared expert is ONE product.  A step of a
+    few tokens reads every expert's weights anyway; a long portion pays experts / top times the products' work for
+    two launches instead of two for every expert and no regrouping of the tokens.  Inner sizes that are no multiple
+    of 8 are zero-padded."""
+
+    graph_safe = True
+
+    def param_specs(self):
+        s, p = self.spec, self.prefix
+        g, u, d = s.names
+        out = {p + s.router_name: ParamSpec((s.experts, s.hidden))}
+        blocks = [(f"{p}{s.expert_prefix}{e}.", s.inter) for e in range(s.experts)]
+        if s.shared_inter:
+            blocks.append((p + s.shared_prefix, s.shared_inter))
+        for prefix, inter in blocks:
+            out[prefix + g] = ParamSpec((inter, s.hidden))
+            out[prefix + u] = ParamSpec((inter, s.hidden))
+            out[prefix + d] = ParamSpec((s.hidden, inter))
+        return out
+
+    def load(self, get) -> None:
+        s, p, rt = self.spec, self.prefix, self.rt
+        g, u, d = s.names
+        self.router = rt.param(get(p + s.router_name), "vector")       # [experts, hidden] in 32-bit
+        self.inter = -(-s.inter // 8) * 8
+        blocks = [(f"{p}{s.expert_prefix}{e}.", s.inter, self.inter) for e in range(s.experts)]
+        if s.shared_inter:
+            blocks.append((p + s.shared_prefix, s.shared_inter, -(-s.shared_inter // 8) * 8))
+        gate_up, down = [], []
+        for prefix, inter, padded in blocks:
+            mats = [rt.param(get(prefix + n)) for n in (g, u, d)]
+            if len({m.dtype for m in mats}) > 1:
+                mats = [m.float() for m in mats]
+            wg, wu, wd = mats
+            if padded != inter:
+                zeros = torch.zeros((padded - inter, s.hidden), dtype=wg.dtype, device=wg.device)
+                wg, wu = torch.cat([wg, zeros]), torch.cat([wu, zeros])
+                wd = torch.cat([wd, torch.zeros((s.hidden, padded - inter), dtype=wd.dtype, device=wd.device)], dim=1)
+            gate_up.append(rt.ops.interleave_gate_up(wg, wu))
+            down.append(wd)
+        if len({m.dtype for m in gate_up + down}) > 1:
+            gate_up, down = [m.float() for m in gate_up], [m.float() for m in down]
+        self.w_gate_up = torch.cat(gate_up, dim=0).contiguous()
+        self.w_down = torch.cat(down, dim=1).contiguous()
+
+    def weight_bytes(self) -> int:
+        return sum(m.numel() * m.element_size() for m in (self.router, self.w_gate_up, self.w_down))
+
+    def first_product(self):
+        return self.rt.ops.product_hint(self.w_gate_up, "silu_mul")
+
+    def forward(self, h, ctx):
+        s, ops = self.spec, self.rt.ops
+        T = h.shape[0]
+        logits = torch.empty((T, s.experts), dtype=torch.float32, device=h.device)
+        ops.linear(h, self.router, None, logits)
+        act = torch.empty((T, self.w_down.shape[1]), dtype=h.dtype, device=h.device)
+        ops.linear_silu_mul(h, self.w_gate_up, act, then=ops.product_hint(self.w_down, "stream"))
+        ops.route_experts(logits, s.top, act, self.inter)
+        return ops.linear_to_stream(act, self.w_down, None, then=self.then)

@@ -15,20 +15,27 @@ class RMSNorm(Norm):
 
     graph_safe = True
     takes_shares = True        # the kernel adds a product's unadded shares while it reads them
+    takes_post = True          # ... and norms and scales the delta first where a layer asks for that
 
     def param_specs(self):
-        return {self.prefix + self.spec.weight_suffix: ParamSpec((self.spec.size,), role="vector", init="one_plus_normal")}
+        init = "normal" if self.spec.one_plus else "one_plus_normal"
+        return {self.prefix + self.spec.weight_suffix: ParamSpec((self.spec.size,), role="vector", init=init)}
 
     def load(self, get) -> None:
         self.weight = self.rt.param(get(self.prefix + self.spec.weight_suffix), "vector")
+        if self.spec.one_plus:          # stored around zero: the kernels multiply with 1 + w, formed once in 32-bit
+            self.weight = (self.weight + 1.0).contiguous()
+
+    def weighted(self):
+        return self.weight
 
     def weight_bytes(self) -> int:
         return self.weight.numel() * self.weight.element_size()
 
-    def __call__(self, x, delta=None, rows=None, status=None):
+    def __call__(self, x, delta=None, rows=None, status=None, post=None):
         n = x.shape[0] if rows is None else rows.numel()
         out = torch.empty((n, self.spec.size), dtype=self.rt.dtype, device=x.device)
-        return self.rt.ops.rmsnorm(x, self.weight, self.spec.eps, out, delta=delta, rows=rows, status=status)
+        return self.rt.ops.rmsnorm(x, self.weight, self.spec.eps, out, delta=delta, rows=rows, status=status, post=post)
 
 
 @register_part("norm", "layernorm")
@@ -36,7 +43,7 @@ class LayerNorm(RMSNorm):
     """out = w * (v - mean(v)) * rsqrt(var(v) + eps) with v = x (+ delta), var the mean of the squared deviations, no
     bias; everything in 32-bit and one rounding at the end.  The kernel is the RMS norm's with the mean taken off."""
 
-    def __call__(self, x, delta=None, rows=None, status=None):
+    def __call__(self, x, delta=None, rows=None, status=None, post=None):
         n = x.shape[0] if rows is None else rows.numel()
         out = torch.empty((n, self.spec.size), dtype=self.rt.dtype, device=x.device)
-        return self.rt.ops.layernorm(x, self.weight, self.spec.eps, out, delta=delta, rows=rows, status=status)
+        return self.rt.ops.layernorm(x, self.weight, self.spec.eps, out, delta=delta, rows=rows, status=status, post=post)

@@ -46,9 +46,23 @@ class NoPosition(PositionEncoding):
         self.table = None
 
 
-def rotation_frequencies(dim: int, base: float) -> torch.Tensor:
-    """[dim / 2] float32: base^(-2i/dim), formed in double and rounded once."""
-    return torch.tensor([math.pow(float(base), -2.0 * i / dim) for i in range(dim // 2)], dtype=torch.float64).to(torch.float32)
+def rotation_frequencies(dim: int, base: float, scaling=None) -> torch.Tensor:
+    """[dim / 2] float32: base^(-2i/dim), formed in double and rounded once.  ``scaling`` = (factor, low, high,
+    original): a frequency f with wavelength l = 2 pi / f stays where l < original / high, becomes f / factor where
+    l > original / low, and between the two (1 - s) f / factor + s f with s = (original / l - low) / (high - low)."""
+    out = []
+    for i in range(dim // 2):
+        f = math.pow(float(base), -2.0 * i / dim)
+        if scaling is not None:
+            factor, low, high, original = (float(v) for v in scaling)
+            wavelength = 2.0 * math.pi / f
+            if wavelength > original / low:
+                f = f / factor
+            elif wavelength >= original / high:
+                s = (original / wavelength - low) / (high - low)
+                f = (1.0 - s) * f / factor + s * f
+        out.append(f)
+    return torch.tensor(out, dtype=torch.float64).to(torch.float32)
 
 
 @register_part("position", "rotary_computed")
@@ -60,4 +74,5 @@ class ComputedRotary(PositionEncoding):
     table = None
 
     def load(self, get) -> None:
-        self.frequencies = rotation_frequencies(self.spec.dim, self.spec.base).to(self.rt.device) if self.spec.dim else None
+        self.frequencies = (rotation_frequencies(self.spec.dim, self.spec.base, self.spec.scaling).to(self.rt.device)
+                            if self.spec.dim else None)

@@ -20,11 +20,13 @@ from typing import Optional, Tuple
 @dataclass(frozen=True)
 class NormSpec:
     """``rmsnorm``: w * x / sqrt(mean(x^2) + eps).  ``layernorm``: w * (x - mean) / sqrt(var + eps), var the mean of
-    the squared deviations, no bias.  ``weight_suffix`` is appended to the part's prefix for the weight's name."""
+    the squared deviations, no bias.  ``weight_suffix`` is appended to the part's prefix for the weight's name.
+    ``one_plus``: the stored weight lies around zero and multiplies as 1 + w."""
     size: int
     eps: float
     kind: str = "rmsnorm"
     weight_suffix: str = ".weight"
+    one_plus: bool = False
 
 
 @dataclass(frozen=True)
@@ -32,11 +34,15 @@ class PositionSpec:
     """``rotary``: rotation of pairs (i, i + dim/2) by pos * base^(-2i/dim), cos and sin from a table of
     ``max_positions`` rows.  ``rotary_computed``: the same rotation of the first ``dim`` dimensions of a head (the
     others pass), the angle formed in 32-bit from the position where it is used: no table, no limit of positions.
-    ``none``: nothing."""
+    ``none``: nothing.
+    ``scaling`` (``rotary_computed``): (factor, low, high, original).  A frequency f with wavelength l = 2 pi / f is kept
+    where l < original / high, divided by factor where l > original / low, and between the two it is
+    (1 - s) f / factor + s f with s = (original / l - low) / (high - low)."""
     dim: int = 0
     base: float = 0.0
     max_positions: int = 0
     kind: str = "rotary"
+    scaling: Optional[Tuple[float, float, float, float]] = None
 
 
 @dataclass(frozen=True)
@@ -65,7 +71,50 @@ class AttentionSpec(MixerSpec):
     v_dim: Optional[int] = None            # size of a head's value where it differs from head_dim (its keys' and queries')
     qk_norm_eps: Optional[float] = None    # e: after the rotation q and k are divided, head by head, by sqrt(mean(.^2) + e)
     chunk: Optional[int] = None            # c: key j is seen from position p only if j // c == p // c (counted from position 0)
+    keep_first: int = 0                    # n: beside the window's keys a token sees the keys at positions below n
     kind: str = "attention"
+
+
+@dataclass(frozen=True)
+class DifferentialAttentionSpec(MixerSpec):
+    """Grouped-query attention whose every head has ``maps`` = 2 sets of queries and keys of ``head_dim`` over one set of
+    values of ``v_dim``.  q [heads, 2, head_dim] and k [kv_heads, 2, head_dim] are divided, map by map, by their root
+    mean square (``norm_eps``) and multiplied by a weight [head_dim] (one for q, one for k, shared by heads and maps),
+    then rotated.  Each map is a softmax attention of its own (``scale``; position p sees j <= p with p - j < ``window``
+    or j < ``keep_first``); with a_1, a_2 their results and lam = exp(lq1 . lk1) - exp(lq2 . lk2) + ``diff`` (four
+    vectors [head_dim], one number a layer): o = (a_1 - lam a_2) / sqrt(mean(.^2) + norm_eps) * (1 - diff) for each head,
+    then the output projection.  ``names``: q, k, v, o, the two norm weights, lq1, lk1, lq2, lk2."""
+    hidden: int = 0
+    heads: int = 0
+    kv_heads: int = 0
+    head_dim: int = 0
+    v_dim: int = 0
+    scale: Optional[float] = None
+    diff: float = 0.0
+    window: Optional[int] = None
+    keep_first: int = 0
+    norm_eps: float = 1e-6
+    position: PositionSpec = field(default_factory=lambda: PositionSpec(kind="none"))
+    names: Tuple[str, ...] = ("q", "k", "v", "o", "q.norm", "k.norm", "lq1", "lk1", "lq2", "lk2")
+    kind: str = "differential_attention"
+
+
+@dataclass(frozen=True)
+class RetentionSpec(MixerSpec):
+    """Linear attention with one fixed decay for each head and no softmax or denominator.  For each head, with
+    S [dim, v_dim] (32-bit, zero at the start of a request): S <- decay[h] S + (k_t / sqrt(dim)) v_t^T, o_t = S^T q_t,
+    q and k rotated by their positions (``position``).  Each head's o is divided by its root mean square
+    (``norm_eps``, no weight) and multiplied by silu(G h); then the output projection.  ``names``: q, k, v, gate,
+    output."""
+    hidden: int = 0
+    heads: int = 0
+    dim: int = 0
+    v_dim: int = 0
+    decay: Tuple[float, ...] = ()
+    norm_eps: float = 1e-6
+    position: PositionSpec = field(default_factory=lambda: PositionSpec(kind="none"))
+    names: Tuple[str, ...] = ("q", "k", "v", "g", "o")
+    kind: str = "retention"
 
 
 @dataclass(frozen=True)
@@ -142,9 +191,28 @@ class PolyNormMLPSpec(FeedForwardSpec):
 
 
 @dataclass(frozen=True)
+class ExpertsSpec(FeedForwardSpec):
+    """A mixture of ``experts`` gated feed-forwards (down(silu(gate(x)) * up(x)), inner size ``inter``, no biases) of
+    which a token uses the ``top`` with the largest router logits z = R x (32-bit), weighted by the softmax over the
+    chosen logits; with ``shared_inter`` an expert of that inner size runs for every token and is added.  Tensors:
+    ``router``, ``e<i>.gate|up|down``, ``shared.gate|up|down`` below the part's prefix."""
+    hidden: int = 0
+    experts: int = 0
+    top: int = 1
+    inter: int = 0
+    shared_inter: Optional[int] = None
+    names: Tuple[str, str, str] = ("gate", "up", "down")
+    router_name: str = "router"
+    expert_prefix: str = "e"
+    shared_prefix: str = "shared."
+    kind: str = "experts"
+
+
+@dataclass(frozen=True)
 class BlockSpec:
     """One layer.  ``prenorm``: x += mixer(norm1(x)); x += ffn(norm2(x)).  With ``ffn`` None the layer has the
-    first sublayer only (and no second norm).
+    first sublayer only (and no second norm).  ``sandwich``: x += m * post1(mixer(norm1(x))); x += m * post2(ffn(norm2(x)))
+    with m = ``residual_mult`` and ``post1``, ``post2`` norms of the sublayers' results.
 
     ``prefix`` is the tensor-name prefix of the layer; ``mixer_prefix`` and the others
     are appended to it for the parts below it."""
@@ -158,6 +226,11 @@ class BlockSpec:
     norm1_name: str = "input_layernorm"
     norm2_name: str = "post_attention_layernorm"
     kind: str = "prenorm"
+    post1: Optional[NormSpec] = None
+    post2: Optional[NormSpec] = None
+    post1_name: str = "norm1b"
+    post2_name: str = "norm2b"
+    residual_mult: float = 1.0
 
 
 @dataclass(frozen=True)
