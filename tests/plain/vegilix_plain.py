@@ -100,28 +100,24 @@ def rotate(x: torch.Tensor, rot: dict, positions: Sequence[int]) -> torch.Tensor
     return out
 
 
-def visible(i: int, j: int, mask: Optional[dict]) -> bool:
-    if j > i:
-        return False
-    if not mask:
-        return True
-    size, keep = mask.get("size"), int(mask.get("keep_first") or 0)
-    return size is None or i - j < int(size) or j < keep
+def visible(T: int, mask: Optional[dict]) -> torch.Tensor:
+    """[T, T] bool: entry (i, j) says whether position i sees position j."""
+    i = torch.arange(T)[:, None]
+    j = torch.arange(T)[None, :]
+    see = j <= i
+    if mask and mask.get("size") is not None:
+        see = see & ((i - j < int(mask["size"])) | (j < int(mask.get("keep_first") or 0)))
+    return see
 
 
 # --------------------------------------------------------------------------- mixers
 
 
 def softmax_map(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, mask: Optional[dict]) -> torch.Tensor:
-    """q [T, d], k [T, d], v [T, dv] of one head and map -> [T, dv]."""
-    T = q.shape[0]
-    out = torch.zeros((T, v.shape[1]), dtype=q.dtype)
-    for i in range(T):
-        js = [j for j in range(i + 1) if visible(i, j, mask)]
-        s = (k[js] @ q[i]) * scale
-        p = torch.softmax(s, dim=0)
-        out[i] = p @ v[js]
-    return out
+    """q [T, d], k [T, d], v [T, dv] of one head and map -> [T, dv]: softmax over the visible keys of every row."""
+    s = (q @ k.T) * scale
+    s = s.masked_fill(~visible(q.shape[0], mask), float("-inf"))
+    return torch.softmax(s, dim=-1) @ v
 
 
 def differential_attention(h: torch.Tensor, W: Dict[str, torch.Tensor], p: str, mc: dict, eps: float,
@@ -172,9 +168,14 @@ def expert(h: torch.Tensor, W: Dict[str, torch.Tensor], p: str) -> torch.Tensor:
     return (silu(h @ W[p + "gate"].T) * (h @ W[p + "up"].T)) @ W[p + "down"].T
 
 
-def experts(h: torch.Tensor, W: Dict[str, torch.Tensor], p: str, fc: dict) -> torch.Tensor:
+def experts(h: torch.Tensor, W: Dict[str, torch.Tensor], p: str, fc: dict, margins: Optional[list] = None) -> torch.Tensor:
+    """``margins`` gets, for every token, how far the last chosen logit lies above the first that is not chosen, as a
+    part of the largest logit's size (a small margin is a close call that rounding may decide the other way)."""
     n, top = int(fc["router"]["experts"]), int(fc["router"]["top"])
     z = h @ W[p + "router"].T                               # [T, n]
+    if margins is not None and top < n:
+        ranked = torch.sort(z, dim=1, descending=True).values
+        margins.append((ranked[:, top - 1] - ranked[:, top]) / z.abs().max(dim=1).values.clamp_min(1e-9))
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         order = sorted(range(n), key=lambda e: (-float(z[t, e]), e))[:top]
@@ -199,8 +200,9 @@ def run_order(cfg: dict) -> List[int]:
 
 
 def forward(cfg: dict, W: Dict[str, torch.Tensor], tokens: Sequence[int], dtype=torch.float64, streams: Optional[list] = None,
-            positions: Optional[Sequence[int]] = None) -> torch.Tensor:
-    """Logits [T, vocab] of one sequence.  ``streams``: a list that gets the residual stream after every layer run."""
+            positions: Optional[Sequence[int]] = None, margins: Optional[list] = None) -> torch.Tensor:
+    """Logits [T, vocab] of one sequence.  ``streams``: a list that gets the residual stream after every layer run;
+    ``margins``: a list that gets every router's margins (see ``experts``)."""
     W = {n: t.to(dtype) for n, t in W.items()}
     eps, m = float(cfg["norm"]["eps"]), float(cfg.get("residual_mult", 1.0))
     pos = list(range(len(tokens))) if positions is None else list(positions)
@@ -217,7 +219,7 @@ def forward(cfg: dict, W: Dict[str, torch.Tensor], tokens: Sequence[int], dtype=
         x = x + m * norm(y, W[p + "norm1b"], eps)
         if layer.get("mlp") is not None:
             h = norm(x, W[p + "norm2"], eps)
-            x = x + m * norm(experts(h, W, p + "mlp.", layer["mlp"]), W[p + "norm2b"], eps)
+            x = x + m * norm(experts(h, W, p + "mlp.", layer["mlp"], margins), W[p + "norm2b"], eps)
         if streams is not None:
             streams.append(x.clone())
     return norm(x, W["final.norm"], eps) @ W["head"].T
