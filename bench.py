@@ -378,10 +378,34 @@ def _sisetar_config(width, ff, gla, att, delta, chunk, pairs=2):
             "logit_scale": 1.0, "logit_softcap": 30.0, "norm": {"eps": 1e-6}}
 
 
+def _vegilix_config(width, ff, ret, att, window, pairs=2):
+    """``pairs`` times (a differential-attention layer, a retention layer), each with 8 experts of which a token uses 2
+    beside a shared expert; the three experts a token runs have ``ff`` inner values together.  ``att``: (heads, kv heads,
+    head size) of the Qwen2 model of equal size: half as many differential heads with two maps of that size over values
+    twice as wide."""
+    heads, kv_heads, dim = att[0] // 2, max(1, att[1] // 2), att[2]
+    mlp = {"kind": "moe", "router": {"experts": 8, "top": 2}, "expert": {"ff": ff // 3 // 64 * 64}, "shared": {"ff": ff // 3 // 64 * 64}}
+    layers = []
+    for _ in range(pairs):
+        layers.append({"type": "attention", "mixer": {
+            "heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": 2 * dim, "diff": 0.3, "scale": dim ** -0.5,
+            "rot": {"dims": dim // 2, "base": 1e6, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}},
+            "mask": {"size": window, "keep_first": 4}}, "mlp": mlp})
+        layers.append({"type": "retention", "mixer": {"heads": ret[0], "dim": ret[1], "vdim": ret[2], "rot": {"dims": ret[1], "base": 1e6},
+                                                      "decay": [1.0 - 2.0 ** (-5 - 0.5 * h) for h in range(ret[0])]}, "mlp": mlp})
+    return {"architecture": "Vegilix", "vocab": 32768, "width": width, "layers": layers, "norm": {"eps": 1e-6}, "residual_mult": 0.7}
+
+
 DESIGN_SIZES = {
     # name: width, feed-forward, (gla heads, dim, vdim), (attention heads, kv heads, head size), (delta heads, dim), chunk
     "w1024": (1024, 4096, (8, 64, 128), (16, 2, 64), (8, 64), 1024),
     "w4096": (4096, 14336, (16, 128, 256), (32, 8, 128), (16, 128), 2048),
+}
+DESIGNS = {
+    # design: how its configuration is made from a row of DESIGN_SIZES
+    "sisetar": lambda width, ff, gla, att, delta, chunk: _sisetar_config(width, ff, gla, att, delta, chunk),
+    # (the recurrent layer has the gated linear attention's sizes; the window is the other design's chunk)
+    "vegilix": lambda width, ff, gla, att, delta, chunk: _vegilix_config(width, ff, gla, att, chunk),
 }
 
 
@@ -390,8 +414,8 @@ def design_points(design: str, sizes, steps: int, warmup: int) -> int:
     ``DESIGN_SIZES``, beside a Qwen2 model of the same width, layer count, feed-forward size and attention heads, and the
     device time of every kernel of one prefill step and one decode step of each (eager, CUDA events around each call;
     the steps that give the throughput run as they are served: prefill eager, decode as captured graphs)."""
-    if design != "sisetar":
-        print(f"bench.py: --design knows 'sisetar', not {design!r}")
+    if design not in DESIGNS:
+        print(f"bench.py: --design knows {', '.join(sorted(DESIGNS))}, not {design!r}")
         return 2
     import torch
     from vt_transformer_b200 import ops
@@ -418,7 +442,7 @@ def design_points(design: str, sizes, steps: int, warmup: int) -> int:
     def per_kernel(runner, entries):
         """Device time of each of the package's kernels in one eager step, by the name of the op."""
         names = [n for n in ("embedding", "rmsnorm", "layernorm", "polynorm", "head_norm_gate", "gla_scan", "delta_scan",
-                             "attention_prepare", "attention_general", "rope_store", "paged_attention", "rope_attention", "linear",
+                             "retention_scan", "route_experts", "attention_prepare", "attention_general", "rope_store", "paged_attention", "rope_attention", "linear",
                              "linear_silu_mul", "linear_to_stream", "logits_scale_cap")]
         saved, events = {n: getattr(ops, n) for n in names}, []
 
@@ -453,7 +477,7 @@ def design_points(design: str, sizes, steps: int, warmup: int) -> int:
         width, ff, gla, att, delta, chunk = DESIGN_SIZES[size]
         vocab = 32768
         models = {
-            "sisetar": _sisetar_config(width, ff, gla, att, delta, chunk),
+            design: DESIGNS[design](width, ff, gla, att, delta, chunk),
             "qwen2": dict(architectures=["Qwen2ForCausalLM"], vocab_size=vocab, hidden_size=width, intermediate_size=ff,
                           num_hidden_layers=4, num_attention_heads=att[0], num_key_value_heads=att[1], head_dim=att[2],
                           rms_norm_eps=1e-6, rope_theta=1e6, max_position_embeddings=8192, tie_word_embeddings=True),
@@ -509,7 +533,7 @@ def design_points(design: str, sizes, steps: int, warmup: int) -> int:
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--design", default=None, help="instead of the default workload: prefill and decode throughput of this design "
-                    "('sisetar') at layer sizes that resemble a served model's, beside a Qwen2 model of equal size")
+                    "('sisetar', 'vegilix') at layer sizes that resemble a served model's, beside a Qwen2 model of equal size")
     ap.add_argument("--design-sizes", default="w1024,w4096", help="which of the sizes of --design to run, with commas between them")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)

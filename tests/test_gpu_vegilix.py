@@ -104,6 +104,48 @@ def test_cuts_equal_the_plain_implementation(vegilix_folders, name, family, dtyp
     cases.replay(vegilix_folders(cases.for_dtype(name, dtype)), cases.prompts_for(name), family, DEV, dtype)
 
 
+@pytest.mark.parametrize("page_size", [16, 64])
+@pytest.mark.parametrize("family", ["whole", "tail", "portions", "mixed"])
+def test_cuts_through_the_tensor_core_attention_kernel(vegilix_folders, family, page_size):
+    """Sizes that the tensor-core kernel of the differential attention takes: bfloat16 runs it for prompt portions and
+    for single tokens (32-bit runs the plain kernel: the same cases, as the oracle's check of the configuration)."""
+    from vt_transformer_b200 import ops
+    assert ops.backend().attention_diff_supports(32, 64, 4, 2) and ops.backend().attention_diff_supports(64, 128, 2, 1)
+    sizes = (40, 3, 64, 2, 150)
+    cases.replay(vegilix_folders("tensor"), cases.prompts_for("tensor"), family, DEV, "bfloat16", sizes=sizes, page_size=page_size, tail=70)
+    if page_size == 16:
+        cases.replay(vegilix_folders("tensor"), cases.prompts_for("tensor"), family, DEV, "float32", sizes=sizes, tail=70)
+
+
+def test_the_windows_edge_and_the_kept_first_tokens_through_the_tensor_core_kernel(vegilix_folders, tmp_path):
+    """A window of 100 that keeps the first 3 tokens, asked from position 250: the marked token just inside and just
+    outside the window (where a block of 64 keys straddles its edge), at the last kept position and the first that is not
+    kept (in a block of its own before the window's); prompt portions and single tokens."""
+    folder = cases.rewritten(vegilix_folders("tensor_alone"), str(tmp_path / "sharp_tc"), lambda t: cases.sharpen_attention(t, 6.0))
+    mask = cases.CONFIGS["tensor_alone"]["layers"][0]["mixer"]["mask"]
+    size, keep = mask["size"], mask["keep_first"]
+    base = cases.prompts_for("tensor_alone", lengths=[262])[0]
+    ask = 250
+    inside, outside = ask - size + 1, ask - size
+    marked = max(range(0, 128, 2), key=lambda tok: _sensitivity(folder, base, ask, inside, tok))
+    kept_mark = max(range(0, 128, 2), key=lambda tok: _sensitivity(folder, base, ask, keep - 1, tok))
+    runner = cases.runner_for(folder, DEV, "bfloat16", num_pages=20, max_requests=1)
+    seen = {}
+    for where, tok in ((inside, marked), (outside, marked), (keep - 1, kept_mark), (keep, kept_mark)):
+        ids = list(base)
+        ids[where] = tok
+        ref = _logits(folder, ids)
+        seen[where] = ref[ask]
+        for cuts in ([len(ids)], [ask, 1, 1, 1], [150, 99, 1, 1, 11], [200, 31]):
+            row = runner.admit()
+            got = cases.step_all(runner, row, ids, cuts)
+            runner.release(row)
+            assert float((got - ref).abs().max()) <= cases.tol("bfloat16", ref, alone=True), (where, cuts)
+    bound = cases.tol("bfloat16", _logits(folder, base), alone=True)
+    assert float((seen[inside] - seen[outside]).abs().max()) > 3 * bound
+    assert float((seen[keep - 1] - seen[keep]).abs().max()) > 3 * bound
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_portions_of_two_tokens_and_pages_of_64(vegilix_folders, dtype):
     folder = vegilix_folders(cases.for_dtype("mix", dtype))

@@ -279,6 +279,41 @@ void attention_general(const Tensor& y, int64_t q_col, Tensor& out, int64_t out_
                                                (float)sub_eps, stream_of(y)), "attention_general");
 }
 
+void attention_diff(const Tensor& y, int64_t q_col, Tensor& out, int64_t out_col, double out_scale, const Tensor& k_cache,
+                    const Tensor& v_cache, const Tensor& cu_q, const Tensor& q_start, const Tensor& block_table,
+                    c10::optional<Tensor> tiles, int64_t heads, int64_t kv_heads, int64_t dim, int64_t v_dim, int64_t window,
+                    int64_t keep_first, double scale, double lam, double sub_eps, c10::optional<Tensor> status) {
+    check_cuda(y, "y"); check_cuda(out, "out"); check_i32(cu_q, "cu_q"); check_i32(q_start, "q_start"); check_i32(block_table, "block_table");
+    TORCH_CHECK(y.scalar_type() == torch::kBFloat16 && out.scalar_type() == torch::kBFloat16, "attention_diff: bfloat16 only");
+    TORCH_CHECK(y.dim() == 2 && out.dim() == 2 && out.size(0) == y.size(0), "attention_diff: y and out [tokens, .]");
+    TORCH_CHECK(block_table.dim() == 2 && cu_q.numel() == q_start.numel() + 1 && block_table.size(0) >= q_start.numel(),
+                "attention_diff: cu_q [sequences + 1], q_start [sequences], block_table [sequences, stride]");
+    TORCH_CHECK(vtb::attention_diff_supports(dim, v_dim, heads, kv_heads), "attention_diff: sizes that the kernel does not take");
+    TORCH_CHECK(q_col % 8 == 0 && out_col % 8 == 0 && y.size(1) % 8 == 0 && out.size(1) % 8 == 0,
+                "attention_diff: columns and rows must start on 16-byte boundaries");
+    check_cols(y, q_col, heads * 2 * dim, "attention_diff (q)"); check_cols(out, out_col, heads * v_dim, "attention_diff (out)");
+    check_pages(k_cache, v_cache, y, kv_heads * 2, dim, v_dim, kv_heads);
+    TORCH_CHECK(k_cache.size(2) % 16 == 0, "attention_diff: pages of a multiple of 16 tokens");
+    const int group = heads / kv_heads;
+    const int per_tile = vtb::attention_diff_tile_rows() / group;
+    const int* tp = nullptr;
+    int n_tiles = q_start.numel();
+    if (tiles.has_value()) {
+        check_i32(*tiles, "tiles");
+        TORCH_CHECK(tiles->dim() == 2 && tiles->size(1) == 2, "attention_diff: tiles [n, 2]");
+        tp = tiles->data_ptr<int>();
+        n_tiles = tiles->size(0);
+    } else {
+        TORCH_CHECK(y.size(0) >= n_tiles, "attention_diff: a step of single tokens has a token for each sequence");
+    }
+    c10::cuda::CUDAGuard guard(y.device());
+    check_launch(vtb::launch_attention_diff(y.data_ptr(), y.size(1), q_col, out.data_ptr(), out.size(1), out_col, (float)out_scale,
+                                            k_cache.data_ptr(), v_cache.data_ptr(), cu_q.data_ptr<int>(), q_start.data_ptr<int>(),
+                                            block_table.data_ptr<int>(), block_table.size(1), tp, n_tiles, per_tile, k_cache.size(0),
+                                            heads, kv_heads, dim, v_dim, k_cache.size(2), window, keep_first, (float)scale, (float)lam,
+                                            (float)sub_eps, status_ptr(status), stream_of(y)), "attention_diff");
+}
+
 void retention_scan(const Tensor& y, int64_t q_col, int64_t k_col, int64_t v_col, const Tensor& decay, double k_scale,
                     c10::optional<Tensor> frequencies, const Tensor& positions, Tensor& state, const Tensor& cu_q, const Tensor& rows,
                     Tensor& o, int64_t heads, int64_t dim, int64_t v_dim, c10::optional<Tensor> status, int64_t most_threads) {
@@ -737,6 +772,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("k_cache"), py::arg("v_cache"), py::arg("positions"), py::arg("token_seq"), py::arg("block_table"), py::arg("heads"),
           py::arg("kv_heads"), py::arg("dim"), py::arg("v_dim"), py::arg("window"), py::arg("chunk"), py::arg("scale"),
           py::arg("status") = py::none(), py::arg("keep_first") = 0, py::arg("maps") = 1, py::arg("lam") = 0.0, py::arg("sub_eps") = 0.0);
+    m.def("attention_diff", &attention_diff);
+    m.def("attention_diff_supports", &vtb::attention_diff_supports);
+    m.def("attention_diff_tile_rows", &vtb::attention_diff_tile_rows);
     m.def("retention_scan", &retention_scan);
     m.def("route_experts", &route_experts);
     m.def("silu_mul", &silu_mul, py::arg("gu"), py::arg("out"), py::arg("interleave") = 0);

@@ -37,6 +37,7 @@ SOURCES = [
     "recurrent.cu",
     "attention_general.cu",
     "experts.cu",
+    "attention_diff.cu",
 ]
 HEADERS = ["common.cuh", "kernels.h", "launch.cuh", "tc_common.cuh", "gemm_epilogue.cuh", "attention_mma.cuh", "attention_decode.cuh", "attention_noalloc.h"]
 

@@ -78,6 +78,17 @@ cudaError_t launch_attention_general(int dtype, const void* y, int stride, int q
                                      int chunk, float scale, int* status, int keep_first, int maps, float lam, float sub_eps,
                                      cudaStream_t stream);
 
+// Differential attention on the tensor cores (attention_diff.cu), bfloat16: the two maps of attention_general with
+// maps 2, for the sizes that attention_diff_supports names.  tiles [n_tiles, 2] (sequence, first token), or null for a
+// step of single tokens (n_tiles = sequences).
+bool attention_diff_supports(int dim, int v_dim, int heads, int kv_heads);
+int attention_diff_tile_rows();
+cudaError_t launch_attention_diff(const void* y, int y_stride, int q_col, void* out, int out_stride, int out_col, float out_scale,
+                                  const void* k_cache, const void* v_cache, const int* cu_q, const int* q_start,
+                                  const int* block_table, int table_stride, const int* tiles, int n_tiles, int tokens_per_tile,
+                                  int n_pages, int heads, int kv_heads, int dim, int v_dim, int page_size, int window,
+                                  int keep_first, float scale, float lam, float sub_eps, int* status, cudaStream_t stream);
+
 // Retention (recurrent.cu): S <- decay[h] S + (k_scale k_t) v_t^T, o_t = S^T q_t for every (sequence, head), q and k
 // rotated (pairs (i, i + half), angle positions[t] * freq[i], 32-bit) while they are staged.
 cudaError_t launch_retention_scan(int dtype, const void* y, int stride, int q_col, int k_col, int v_col, const float* decay,

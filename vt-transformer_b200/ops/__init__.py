@@ -222,6 +222,29 @@ def attention_general(y, q_col: int, out, out_col: int, out_scale: float, k_cach
     return out
 
 
+def attention_differential(y, q_col: int, out, out_col: int, out_scale: float, k_cache, v_cache, ctx, block_table, heads: int,
+                           kv_heads: int, dim: int, v_dim: int, window, keep_first: int, scale: float, lam: float, sub_eps: float,
+                           status=None):
+    """Differential attention of the step's tokens over the paged keys and values of their sequences: every head has
+    two queries [2, dim] (at column ``q_col`` of ``y``) and every head of values two heads of keys; with a_1, a_2 the two
+    softmax attentions over the same values, out[t, out_col + h * v_dim + :] = out_scale * o / sqrt(mean(o^2) + sub_eps),
+    o = a_1 - lam * a_2.  Position p sees j <= p with p - j < window or j < keep_first.  bfloat16 at the sizes the
+    tensor-core kernel takes runs that kernel (prompt portions in tiles of 64 rows of (token, head of the group);
+    single tokens a CTA for each (sequence, head of values)); everything else, and all of float32, the plain kernel."""
+    be = backend()
+    if (y.dtype == torch.bfloat16 and ATTENTION_KERNEL in ("auto", "mma") and k_cache.shape[2] % 16 == 0 and q_col % 8 == 0
+            and out_col % 8 == 0 and be.attention_diff_supports(int(dim), int(v_dim), int(heads), int(kv_heads))):
+        singles = ctx.max_q_len == 1 and ctx.n_tokens == ctx.n_seqs
+        tiles = None if singles else _attention_tiles(ctx, be.attention_diff_tile_rows() // (heads // kv_heads), y.device)
+        be.attention_diff(y, int(q_col), out, int(out_col), float(out_scale), k_cache, v_cache, ctx.cu_q, ctx.q_start, block_table,
+                          tiles, int(heads), int(kv_heads), int(dim), int(v_dim), int(window) if window else 0, int(keep_first),
+                          float(scale), float(lam), float(sub_eps), status)
+        return out
+    return attention_general.__wrapped__(y, q_col, out, out_col, out_scale, k_cache, v_cache, ctx, block_table, heads, kv_heads, dim,
+                                         v_dim, window, None, scale, status=status, keep_first=keep_first, maps=2, lam=lam,
+                                         sub_eps=sub_eps)
+
+
 def route_experts(logits: torch.Tensor, top: int, act: torch.Tensor, inter: int) -> torch.Tensor:
     """For every token (row): the ``top`` largest of its router logits [experts] (float32; the lower index among
     equals) choose its experts, the softmax over the chosen logits weighs them; columns [e * inter, (e + 1) * inter) of
@@ -666,6 +689,6 @@ def _counted(fn):
     return wrapper
 
 
-for _name in ("embedding", "logits_scale_cap", "rmsnorm", "layernorm", "polynorm", "scale_into", "head_norm_gate", "gla_scan", "delta_scan", "retention_scan", "route_experts",
+for _name in ("embedding", "logits_scale_cap", "rmsnorm", "layernorm", "polynorm", "scale_into", "head_norm_gate", "gla_scan", "delta_scan", "retention_scan", "route_experts", "attention_differential",
               "attention_prepare", "attention_general", "silu_mul", "rope_store", "linear", "paged_attention", "argmax", "sample"):  # the others count where they launch
     globals()[_name] = _counted(globals()[_name])

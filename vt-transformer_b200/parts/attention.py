@@ -256,6 +256,6 @@ class DifferentialAttention(ProjectedMixer):
         ops.attention_prepare(y, cols[0], cols[1], cols[2], ctx, freq, s.norm_eps, k_pages, v_pages, cache.block_table,
                               s.heads * 2, s.kv_heads * 2, s.head_dim, s.v_dim, store=cache.writes, status=ctx.status,
                               v_heads=s.kv_heads, q_weight=self.q_weight, k_weight=self.k_weight, norm_first=True)
-        ops.attention_general(y, cols[0], out, out_col, out_scale * (1.0 - s.diff), k_pages, v_pages, ctx, cache.block_table,
-                              s.heads, s.kv_heads, s.head_dim, s.v_dim, s.window, None, self.scale, status=ctx.status,
-                              keep_first=self.keep_first, maps=2, lam=self.lam, sub_eps=s.norm_eps)
+        ops.attention_differential(y, cols[0], out, out_col, out_scale * (1.0 - s.diff), k_pages, v_pages, ctx, cache.block_table,
+                                   s.heads, s.kv_heads, s.head_dim, s.v_dim, s.window, self.keep_first, self.scale, self.lam,
+                                   s.norm_eps, status=ctx.status)
