@@ -442,7 +442,7 @@ def design_points(design: str, sizes, steps: int, warmup: int) -> int:
     def per_kernel(runner, entries):
         """Device time of each of the package's kernels in one eager step, by the name of the op."""
         names = [n for n in ("embedding", "rmsnorm", "layernorm", "polynorm", "head_norm_gate", "gla_scan", "delta_scan",
-                             "retention_scan", "route_experts", "attention_prepare", "attention_general", "rope_store", "paged_attention", "rope_attention", "linear",
+                             "retention_scan", "route_experts", "attention_differential", "attention_prepare", "attention_general", "rope_store", "paged_attention", "rope_attention", "linear",
                              "linear_silu_mul", "linear_to_stream", "logits_scale_cap")]
         saved, events = {n: getattr(ops, n) for n in names}, []
 
