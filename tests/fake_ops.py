@@ -332,3 +332,36 @@ def route_experts(logits, top, act, inter):
         w[t, order] = torch.softmax(logits[t, order], dim=0)
     scaled = act[:, :n * inter].float().view(T, n, inter) * w[:, :, None]
     act[:, :n * inter] = torch.where(w[:, :, None] > 0, scaled, torch.zeros_like(scaled)).reshape(T, n * inter).to(act.dtype)
+
+
+def route_topk(logits, top, ids, weights):
+    for t in range(logits.shape[0]):
+        order = sorted(range(logits.shape[1]), key=lambda e: (-float(logits[t, e]), e))[:top]
+        ids[t] = torch.tensor(order, dtype=torch.int32)
+        weights[t] = torch.softmax(logits[t, order], dim=0)
+
+
+def expert_lists(ids, lists, counts):
+    flat = ids.reshape(-1)
+    for e in range(lists.shape[0]):
+        mine = torch.nonzero(flat == e).flatten().to(torch.int32)
+        lists[e, :mine.numel()] = mine
+        counts[e] = mine.numel()
+
+
+def gather_picks(x, lists, counts, top, rows, where):
+    r = 0
+    for e in range(lists.shape[0]):
+        for i in range(int(counts[e])):
+            pick = int(lists[e, i])
+            rows[r] = x[pick // top]
+            where[pick] = r
+            r += 1
+
+
+def combine_picks(y, where, weights, shared_y, out):
+    T, top = weights.shape
+    acc = (weights[:, :, None] * y[where.long()].float().view(T, top, -1)).sum(dim=1)
+    if shared_y is not None:
+        acc = acc + shared_y.float()
+    out.copy_(acc.to(out.dtype))

@@ -104,6 +104,20 @@ def test_cuts_equal_the_plain_implementation(vegilix_folders, name, family, dtyp
     cases.replay(vegilix_folders(cases.for_dtype(name, dtype)), cases.prompts_for(name), family, DEV, dtype)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["mix", "wide", "experts_alone"])
+def test_tokens_grouped_by_expert(vegilix_folders, monkeypatch, name, dtype):
+    """Portions with many picks group their tokens by expert (the experts' products over slices of sorted rows) instead of
+    running every expert on every token: forced here for every portion, also those in which an expert gets no token."""
+    from vt_transformer_b200 import ops
+    monkeypatch.setattr(ops, "EXPERTS_GROUPED_MIN_PICKS", 1)
+    folder = vegilix_folders(cases.for_dtype(name, dtype) if name != "experts_alone" else name)
+    before = ops.launches
+    for family in ("whole", "portions", "mixed"):
+        cases.replay(folder, cases.prompts_for(name), family, DEV, dtype)
+    assert ops.launches > before
+
+
 @pytest.mark.parametrize("page_size", [16, 64])
 @pytest.mark.parametrize("family", ["whole", "tail", "portions", "mixed"])
 def test_cuts_through_the_tensor_core_attention_kernel(vegilix_folders, family, page_size):

@@ -101,6 +101,14 @@ def test_cuts_equal_the_plain_implementation(fake_backend, vegilix_folders, fami
     cases.replay(vegilix_folders("mix"), cases.prompts_for("mix"), family, "cpu", "float32")
 
 
+def test_tokens_grouped_by_expert_equal_the_plain_implementation(fake_backend, vegilix_folders, monkeypatch):
+    from vt_transformer_b200 import ops
+    monkeypatch.setattr(ops, "EXPERTS_GROUPED_MIN_PICKS", 1)
+    for name in ("mix", "experts_alone"):
+        cases.replay(vegilix_folders(name), cases.prompts_for(name), "portions", "cpu", "float32")
+        cases.replay(vegilix_folders(name), cases.prompts_for(name), "mixed", "cpu", "float32")
+
+
 def test_a_span_repeated_from_the_first_layer(fake_backend, vegilix_folders):
     cases.replay(vegilix_folders("looped_start"), cases.prompts_for("looped_start"), "mixed", "cpu", "float32")
 

@@ -77,6 +77,7 @@ attention_diff_kernel(const DiffParams p) {
         return;
     }
     const int rows_valid = ntok * group;
+    const bool slab_live = rg * 16 < rows_valid;
     const int start = p.q_start[seq];
     const int pos_lo = start + tok0, pos_hi = pos_lo + ntok - 1;
     const int keep = p.window > 0 ? p.keep_first : 0;
@@ -123,37 +124,42 @@ attention_diff_kernel(const DiffParams p) {
         const int kb = first_key_of(blk);
         // the block's four runs of 16 keys lie in one page each
         static_assert(KB == 64, "four runs of 16 keys");
-        int page_of[4];
+        size_t base_k[4], base_v[4];      // rows of the run's first key (map 0) and first value in the pages
         bool okp[4];
 #pragma unroll
         for (int h = 0; h < 4; ++h) {
             const int key = kb + 16 * h;
             okp[h] = key < key_hi;
-            page_of[h] = 0;
+            base_k[h] = base_v[h] = 0;
             if (okp[h]) {
                 const int page = table[key / p.page_size];
                 // a page between the kept first tokens and the window may be gone already; its keys are masked below
-                if (page < 0 || page >= p.n_pages) okp[h] = false;
-                else page_of[h] = page;
+                if (page < 0 || page >= p.n_pages) {
+                    okp[h] = false;
+                } else {
+                    const size_t pv = (size_t)page * p.kv_heads + kvh;
+                    base_v[h] = pv * p.page_size + key % p.page_size;
+                    base_k[h] = pv * 2 * p.page_size + key % p.page_size;
+                }
             }
         }
         constexpr int KC = D / 8, VC = DV / 8;          // 16-byte pieces in a row of keys, of values
         for (int c = threadIdx.x; c < 2 * KB * KC; c += THREADS) {
             const int m = c / (KB * KC), r = (c / KC) % KB, piece = c % KC;
-            const int h = r >> 4;
-            const int page = h == 0 ? page_of[0] : h == 1 ? page_of[1] : h == 2 ? page_of[2] : page_of[3];
+            const int h = r >> 4;                       // selected without indexing, so the bases stay in registers
+            const size_t bh = h == 0 ? base_k[0] : h == 1 ? base_k[1] : h == 2 ? base_k[2] : base_k[3];
             const bool oh = h == 0 ? okp[0] : h == 1 ? okp[1] : h == 2 ? okp[2] : okp[3];
             const bool ok = oh && (kb + r) < key_hi;
-            const size_t off = ok ? ((((size_t)page * p.kv_heads + kvh) * 2 + m) * p.page_size + (kb + r) % p.page_size) * D + piece * 8 : 0;
+            const size_t off = ok ? (bh + (size_t)m * p.page_size + (r & 15)) * D + piece * 8 : 0;
             cp_async16(ks + (((size_t)stage * 2 + m) * KB + r) * LD + piece * 8, p.k_cache + off, ok);
         }
         for (int c = threadIdx.x; c < KB * VC; c += THREADS) {
             const int r = c / VC, piece = c % VC;
             const int h = r >> 4;
-            const int page = h == 0 ? page_of[0] : h == 1 ? page_of[1] : h == 2 ? page_of[2] : page_of[3];
+            const size_t bh = h == 0 ? base_v[0] : h == 1 ? base_v[1] : h == 2 ? base_v[2] : base_v[3];
             const bool oh = h == 0 ? okp[0] : h == 1 ? okp[1] : h == 2 ? okp[2] : okp[3];
             const bool ok = oh && (kb + r) < key_hi;
-            const size_t off = ok ? (((size_t)page * p.kv_heads + kvh) * p.page_size + (kb + r) % p.page_size) * DV + piece * 8 : 0;
+            const size_t off = ok ? (bh + (r & 15)) * DV + piece * 8 : 0;
             cp_async16(vs + ((size_t)stage * KB + r) * LDV + piece * 8, p.v_cache + off, ok);
         }
     };
@@ -170,6 +176,10 @@ attention_diff_kernel(const DiffParams p) {
             cp_async_wait<0>();
         }
         __syncthreads();
+        if (!slab_live) {                                // a slab without rows (a short tile): copies and barriers only
+            __syncthreads();
+            continue;
+        }
         const __nv_bfloat16* kst = ks + ((size_t)stage * 2 + map) * KB * LD;
         const __nv_bfloat16* vst = vs + (size_t)stage * KB * LDV;
         const int kb = first_key_of(blk);

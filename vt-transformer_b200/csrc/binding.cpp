@@ -338,6 +338,52 @@ void retention_scan(const Tensor& y, int64_t q_col, int64_t k_col, int64_t v_col
                                             v_dim, (int)most_threads, status_ptr(status), stream_of(y)), "retention_scan");
 }
 
+void route_topk(const Tensor& logits, int64_t top, Tensor& ids, Tensor& weights) {
+    check_f32(logits, "logits"); check_i32(ids, "ids"); check_f32(weights, "weights");
+    TORCH_CHECK(logits.dim() == 2 && ids.dim() == 2 && ids.size(0) == logits.size(0) && ids.size(1) == top && weights.sizes() == ids.sizes(),
+                "route_topk: logits [tokens, experts], ids and weights [tokens, top]");
+    TORCH_CHECK(logits.size(1) <= 1024 && top >= 1 && top <= logits.size(1), "route_topk: 1 <= top <= experts <= 1024");
+    c10::cuda::CUDAGuard guard(logits.device());
+    check_launch(vtb::launch_route_topk(logits.data_ptr<float>(), logits.size(0), logits.size(1), top, ids.data_ptr<int>(),
+                                        weights.data_ptr<float>(), stream_of(logits)), "route_topk");
+}
+
+void expert_lists(const Tensor& ids, Tensor& lists, Tensor& counts) {
+    check_i32(ids, "ids"); check_i32(lists, "lists"); check_i32(counts, "counts");
+    TORCH_CHECK(lists.dim() == 2 && counts.numel() == lists.size(0) && lists.size(1) >= ids.size(0),
+                "expert_lists: lists [experts, at least tokens], counts [experts]");
+    c10::cuda::CUDAGuard guard(ids.device());
+    check_launch(vtb::launch_expert_lists(ids.data_ptr<int>(), ids.numel(), lists.size(0), lists.size(1), lists.data_ptr<int>(),
+                                          counts.data_ptr<int>(), stream_of(ids)), "expert_lists");
+}
+
+void gather_picks(const Tensor& x, const Tensor& lists, const Tensor& counts, int64_t top, Tensor& sorted, Tensor& where) {
+    check_cuda(x, "x"); check_cuda(sorted, "sorted"); check_i32(lists, "lists"); check_i32(counts, "counts"); check_i32(where, "where");
+    TORCH_CHECK(x.dim() == 2 && sorted.dim() == 2 && sorted.size(1) == x.size(1) && sorted.size(0) == x.size(0) * top &&
+                where.numel() == sorted.size(0) && x.scalar_type() == sorted.scalar_type() && x.size(1) % 8 == 0,
+                "gather_picks: x [tokens, width], sorted [tokens * top, width], where [tokens * top]");
+    c10::cuda::CUDAGuard guard(x.device());
+    check_launch(vtb::launch_gather_picks(dtype_code(x, "x"), x.data_ptr(), x.size(1), lists.data_ptr<int>(), lists.size(1),
+                                          counts.data_ptr<int>(), lists.size(0), top, sorted.size(0), sorted.data_ptr(),
+                                          where.data_ptr<int>(), stream_of(x)), "gather_picks");
+}
+
+void combine_picks(const Tensor& y, const Tensor& where, const Tensor& weights, c10::optional<Tensor> shared_y, Tensor& out) {
+    check_cuda(y, "y"); check_cuda(out, "out"); check_i32(where, "where"); check_f32(weights, "weights");
+    TORCH_CHECK(weights.dim() == 2 && out.dim() == 2 && y.dim() == 2 && out.size(0) == weights.size(0) && y.size(1) == out.size(1) &&
+                y.size(0) == where.numel() && where.numel() == weights.numel() && y.scalar_type() == out.scalar_type() && out.size(1) % 8 == 0,
+                "combine_picks: y [tokens * top, width], where [tokens * top], weights [tokens, top], out [tokens, width]");
+    const void* sp = nullptr;
+    if (shared_y.has_value()) {
+        check_cuda(*shared_y, "shared_y");
+        TORCH_CHECK(shared_y->sizes() == out.sizes() && shared_y->scalar_type() == out.scalar_type(), "combine_picks: shared_y like out");
+        sp = shared_y->data_ptr();
+    }
+    c10::cuda::CUDAGuard guard(y.device());
+    check_launch(vtb::launch_combine_picks(dtype_code(y, "y"), y.data_ptr(), y.size(1), where.data_ptr<int>(), weights.data_ptr<float>(),
+                                           weights.size(1), out.size(0), sp, out.data_ptr(), stream_of(y)), "combine_picks");
+}
+
 void route_experts(const Tensor& logits, int64_t top, Tensor& act, int64_t inter) {
     check_f32(logits, "logits"); check_cuda(act, "act");
     TORCH_CHECK(logits.dim() == 2 && act.dim() == 2 && act.size(0) == logits.size(0), "route_experts: logits [tokens, experts], act [tokens, .]");
@@ -777,6 +823,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("attention_diff_tile_rows", &vtb::attention_diff_tile_rows);
     m.def("retention_scan", &retention_scan);
     m.def("route_experts", &route_experts);
+    m.def("route_topk", &route_topk);
+    m.def("expert_lists", &expert_lists);
+    m.def("gather_picks", &gather_picks);
+    m.def("combine_picks", &combine_picks);
     m.def("silu_mul", &silu_mul, py::arg("gu"), py::arg("out"), py::arg("interleave") = 0);
     m.def("rope_store", &rope_store, py::arg("qkv"), py::arg("positions"), py::arg("cos_sin"), py::arg("k_cache"),
           py::arg("v_cache"), py::arg("token_seq"), py::arg("block_table"), py::arg("heads"), py::arg("kv_heads"),

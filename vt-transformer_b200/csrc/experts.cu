@@ -5,6 +5,11 @@
 // block a token: a warp picks the `top` largest router logits (32-bit; the lower index among equals), forms the softmax
 // over the picked logits, and the block multiplies the picked experts' columns of the activation by their weights and
 // clears the others', so that the second product adds up exactly the chosen experts' results.
+//
+// For long portions the picks are grouped instead: `route_topk` leaves each token's picks and weights, `expert_lists`
+// the picks of every expert in rising order (one block an expert, no atomics: the order is fixed), `gather_picks` the
+// input rows sorted by expert, and after the experts' products over their slices `combine_picks` adds a token's picks
+// in the order of the picks, in 32-bit.
 #include "common.cuh"
 #include "kernels.h"
 #include "launch.cuh"
@@ -14,6 +19,43 @@ namespace vtb {
 namespace {
 constexpr int kMaxExperts = 1024;
 constexpr int kRouteThreads = 128;
+}
+
+// The `top` largest of z[0 .. experts) (the lower index among equals), by the first warp of the block: picked[k] and
+// picked_z[k] in falling order; z is used up.  Then w[e] = softmax over the picked logits (0 for the others) if w is given.
+__device__ __forceinline__ void pick_top(float* z, float* w, int* picked, float* picked_z, int experts, int top) {
+    const int lane = threadIdx.x & 31;
+    if (threadIdx.x >= 32) return;
+    for (int k = 0; k < top; ++k) {
+        float best = -INFINITY;
+        int at = 0x7fffffff;
+        for (int e = lane; e < experts; e += 32) {
+            const float v = z[e];
+            if (at == 0x7fffffff || v > best) { best = v; at = e; }      // a lane meets its experts in rising order
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+            if (oa != 0x7fffffff && (at == 0x7fffffff || ov > best || (ov == best && oa < at))) { best = ov; at = oa; }
+        }
+        if (lane == 0) {
+            picked[k] = at;
+            picked_z[k] = best;
+            z[at] = -INFINITY;
+        }
+        __syncwarp();
+    }
+    if (lane == 0) {
+        const float mx = picked_z[0];                  // the first pick is the largest
+        float sum = 0.f;
+        for (int k = 0; k < top; ++k) sum += expf(picked_z[k] - mx);
+        for (int k = 0; k < top; ++k) {
+            const float wk = expf(picked_z[k] - mx) / sum;
+            picked_z[k] = wk;                          // from here on: the pick's weight
+            if (w) w[picked[k]] = wk;
+        }
+    }
 }
 
 template <typename T>
@@ -26,40 +68,12 @@ route_experts_kernel(const float* __restrict__ logits, int experts, int top, T* 
     pdl_launch();
     pdl_wait();
     const int t = blockIdx.x;
-    const int lane = threadIdx.x & 31;
     for (int e = threadIdx.x; e < experts; e += blockDim.x) {
         z[e] = logits[(size_t)t * experts + e];
         w[e] = 0.f;
     }
     __syncthreads();
-    if (threadIdx.x < 32) {
-        for (int k = 0; k < top; ++k) {
-            float best = -INFINITY;
-            int at = 0x7fffffff;
-            for (int e = lane; e < experts; e += 32) {
-                const float v = z[e];
-                if (at == 0x7fffffff || v > best) { best = v; at = e; }      // a lane meets its experts in rising order
-            }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-                const int oa = __shfl_xor_sync(0xffffffffu, at, o);
-                if (oa != 0x7fffffff && (at == 0x7fffffff || ov > best || (ov == best && oa < at))) { best = ov; at = oa; }
-            }
-            if (lane == 0) {
-                picked[k] = at;
-                picked_z[k] = best;
-                z[at] = -INFINITY;
-            }
-            __syncwarp();
-        }
-        if (lane == 0) {
-            const float mx = picked_z[0];                  // the first pick is the largest
-            float sum = 0.f;
-            for (int k = 0; k < top; ++k) sum += expf(picked_z[k] - mx);
-            for (int k = 0; k < top; ++k) w[picked[k]] = expf(picked_z[k] - mx) / sum;
-        }
-    }
+    pick_top(z, w, picked, picked_z, experts, top);
     __syncthreads();
     T* row = act + (size_t)t * act_stride;
     if (inter % 8 == 0 && act_stride % 8 == 0 && (reinterpret_cast<uintptr_t>(act) & 15) == 0) {
@@ -83,6 +97,142 @@ route_experts_kernel(const float* __restrict__ logits, int experts, int top, T* 
         const float we = w[c / inter];
         row[c] = from_float<T>(we > 0.f ? to_float(row[c]) * we : 0.f);
     }
+}
+
+// The picks themselves: ids[t, k] and weights[t, k] in falling order of the logits (for the grouped products).
+__global__ void __launch_bounds__(32)
+route_topk_kernel(const float* __restrict__ logits, int experts, int top, int* __restrict__ ids, float* __restrict__ weights) {
+    __shared__ float z[kMaxExperts];
+    __shared__ float picked_z[kMaxExperts];
+    __shared__ int picked[kMaxExperts];
+    pdl_launch();
+    pdl_wait();
+    const int t = blockIdx.x;
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) z[e] = logits[(size_t)t * experts + e];
+    __syncwarp();
+    pick_top(z, nullptr, picked, picked_z, experts, top);
+    __syncwarp();
+    for (int k = threadIdx.x; k < top; k += blockDim.x) {
+        ids[(size_t)t * top + k] = picked[k];
+        weights[(size_t)t * top + k] = picked_z[k];
+    }
+}
+
+// One block an expert: the picks (flat index t * top + k) that chose it, in rising order, into lists[e, 0 .. counts[e]).
+__global__ void __launch_bounds__(256)
+expert_lists_kernel(const int* __restrict__ ids, int n_picks, int list_stride, int* __restrict__ lists, int* __restrict__ counts) {
+    __shared__ int warp_total[8];
+    __shared__ int running;
+    pdl_launch();
+    pdl_wait();
+    const int e = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (threadIdx.x == 0) running = 0;
+    __syncthreads();
+    for (int base = 0; base < n_picks; base += 256) {
+        const int i = base + threadIdx.x;
+        const bool mine = i < n_picks && ids[i] == e;
+        const unsigned vote = __ballot_sync(0xffffffffu, mine);
+        if (lane == 0) warp_total[warp] = __popc(vote);
+        __syncthreads();
+        int before = running;
+        for (int w = 0; w < warp; ++w) before += warp_total[w];
+        if (mine) lists[(size_t)e * list_stride + before + __popc(vote & ((1u << lane) - 1u))] = i;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int total = 0;
+            for (int w = 0; w < 8; ++w) total += warp_total[w];
+            running += total;
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) counts[e] = running;
+}
+
+// Row r of the sorted rows (expert by expert, each in the order of its list) is the input row of its pick's token;
+// where[pick] = r tells the combining kernel where the pick's result lies.
+template <typename T>
+__global__ void __launch_bounds__(128)
+gather_picks_kernel(const T* __restrict__ x, int width, const int* __restrict__ lists, int list_stride, const int* __restrict__ counts,
+                    int experts, int top, T* __restrict__ sorted, int* __restrict__ where) {
+    __shared__ int src;
+    pdl_launch();
+    pdl_wait();
+    const int r = blockIdx.x;
+    if (threadIdx.x == 0) {
+        int e = 0, off = 0;
+        while (e < experts && off + counts[e] <= r) off += counts[e++];
+        src = e < experts ? lists[(size_t)e * list_stride + (r - off)] : -1;
+        if (src >= 0) where[src] = r;
+    }
+    __syncthreads();
+    if (src < 0) return;
+    const T* from = x + (size_t)(src / top) * width;
+    T* to = sorted + (size_t)r * width;
+    for (int c = threadIdx.x * 8; c < width; c += blockDim.x * 8) {
+        float v[8];
+        Vec8<T>::load(from + c, v);
+        Vec8<T>::store(to + c, v);
+    }
+}
+
+// out[t] = sum_k weights[t, k] * y[where[t * top + k]] (+ shared[t]) in 32-bit, in the order of k, one rounding.
+template <typename T>
+__global__ void __launch_bounds__(128)
+combine_picks_kernel(const T* __restrict__ y, int width, const int* __restrict__ where, const float* __restrict__ weights, int top,
+                     const T* __restrict__ shared_y, T* __restrict__ out) {
+    pdl_launch();
+    pdl_wait();
+    const int t = blockIdx.x;
+    for (int c = threadIdx.x * 8; c < width; c += blockDim.x * 8) {
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int k = 0; k < top; ++k) {
+            const float wk = weights[(size_t)t * top + k];
+            float v[8];
+            Vec8<T>::load(y + (size_t)where[(size_t)t * top + k] * width + c, v);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] = fmaf(wk, v[j], acc[j]);
+        }
+        if (shared_y != nullptr) {
+            float v[8];
+            Vec8<T>::load(shared_y + (size_t)t * width + c, v);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] += v[j];
+        }
+        Vec8<T>::store(out + (size_t)t * width + c, acc);
+    }
+}
+
+cudaError_t launch_route_topk(const float* logits, int n_tokens, int experts, int top, int* ids, float* weights, cudaStream_t stream) {
+    if (n_tokens == 0) return cudaSuccess;
+    if (experts < 1 || experts > kMaxExperts || top < 1 || top > experts) return cudaErrorInvalidValue;
+    return launch(route_topk_kernel, n_tokens, 32, 0, stream, logits, experts, top, ids, weights);
+}
+
+cudaError_t launch_expert_lists(const int* ids, int n_picks, int experts, int list_stride, int* lists, int* counts, cudaStream_t stream) {
+    if (experts == 0) return cudaSuccess;
+    return launch(expert_lists_kernel, experts, 256, 0, stream, ids, n_picks, list_stride, lists, counts);
+}
+
+cudaError_t launch_gather_picks(int dtype, const void* x, int width, const int* lists, int list_stride, const int* counts, int experts,
+                                int top, int n_picks, void* sorted, int* where, cudaStream_t stream) {
+    if (n_picks == 0) return cudaSuccess;
+    if (width % 8) return cudaErrorInvalidValue;
+    if (dtype == kBF16)
+        return launch(gather_picks_kernel<__nv_bfloat16>, n_picks, 128, 0, stream, (const __nv_bfloat16*)x, width, lists, list_stride,
+                      counts, experts, top, (__nv_bfloat16*)sorted, where);
+    return launch(gather_picks_kernel<float>, n_picks, 128, 0, stream, (const float*)x, width, lists, list_stride, counts, experts, top,
+                  (float*)sorted, where);
+}
+
+cudaError_t launch_combine_picks(int dtype, const void* y, int width, const int* where, const float* weights, int top, int n_tokens,
+                                 const void* shared_y, void* out, cudaStream_t stream) {
+    if (n_tokens == 0) return cudaSuccess;
+    if (width % 8) return cudaErrorInvalidValue;
+    if (dtype == kBF16)
+        return launch(combine_picks_kernel<__nv_bfloat16>, n_tokens, 128, 0, stream, (const __nv_bfloat16*)y, width, where, weights, top,
+                      (const __nv_bfloat16*)shared_y, (__nv_bfloat16*)out);
+    return launch(combine_picks_kernel<float>, n_tokens, 128, 0, stream, (const float*)y, width, where, weights, top,
+                  (const float*)shared_y, (float*)out);
 }
 
 cudaError_t launch_route_experts(int dtype, const float* logits, int n_tokens, int experts, int top, void* act, int act_stride,

@@ -101,6 +101,15 @@ cudaError_t launch_retention_scan(int dtype, const void* y, int stride, int q_co
 // act [n_tokens, act_stride] of `dtype`.
 cudaError_t launch_route_experts(int dtype, const float* logits, int n_tokens, int experts, int top, void* act, int act_stride,
                                  int inter, cudaStream_t stream);
+// The grouped form: ids / weights [n_tokens, top] of each token's picks; lists [experts, list_stride] of the picks (flat
+// index t * top + k) of every expert in rising order and counts [experts]; sorted [n_picks, width] the input rows by
+// expert and where [n_picks] each pick's row; out[t] = sum_k weights[t, k] * y[where[t * top + k]] (+ shared_y[t]).
+cudaError_t launch_route_topk(const float* logits, int n_tokens, int experts, int top, int* ids, float* weights, cudaStream_t stream);
+cudaError_t launch_expert_lists(const int* ids, int n_picks, int experts, int list_stride, int* lists, int* counts, cudaStream_t stream);
+cudaError_t launch_gather_picks(int dtype, const void* x, int width, const int* lists, int list_stride, const int* counts, int experts,
+                                int top, int n_picks, void* sorted, int* where, cudaStream_t stream);
+cudaError_t launch_combine_picks(int dtype, const void* y, int width, const int* where, const float* weights, int top, int n_tokens,
+                                 const void* shared_y, void* out, cudaStream_t stream);
 
 // dst[t, dst_col + i] = scale * src[t, i] for src [n_tokens, n] and dst [n_tokens, dst_stride], the product in 32-bit.
 cudaError_t launch_scale_into(int dtype, const void* src, void* dst, int n_tokens, int n, int dst_stride, int dst_col, float scale,

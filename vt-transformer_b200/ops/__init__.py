@@ -222,6 +222,35 @@ def attention_general(y, q_col: int, out, out_col: int, out_scale: float, k_cach
     return out
 
 
+# Picks (tokens of a step times the experts each uses) from which a mixture of experts groups its tokens by expert
+# instead of running every expert on every token.  Below it, and in every step of single tokens, the two packed
+# products read each expert's weights once, which a small batch does anyway, and the step stays a CUDA graph.
+EXPERTS_GROUPED_MIN_PICKS = int(os.environ.get("VTB200_EXPERTS_GROUPED_MIN_PICKS", "1024"))
+
+
+def route_topk(logits: torch.Tensor, top: int, ids: torch.Tensor, weights: torch.Tensor) -> None:
+    """ids[t, k] and weights[t, k]: the ``top`` largest router logits of every token in falling order (the lower index
+    among equals) and the softmax over them."""
+    backend().route_topk(logits, int(top), ids, weights)
+
+
+def expert_lists(ids: torch.Tensor, lists: torch.Tensor, counts: torch.Tensor) -> None:
+    """lists[e, :counts[e]]: the picks (flat index t * top + k of ``ids``) that chose expert e, in rising order."""
+    backend().expert_lists(ids, lists, counts)
+
+
+def gather_picks(x: torch.Tensor, lists: torch.Tensor, counts: torch.Tensor, top: int, rows: torch.Tensor, where: torch.Tensor) -> None:
+    """rows: the rows of x sorted by expert (expert 0's picks in the order of its list, then expert 1's, ...), row of pick
+    p being x[p // top]; where[p]: the row at which pick p lies."""
+    backend().gather_picks(x, lists, counts, int(top), rows, where)
+
+
+def combine_picks(y: torch.Tensor, where: torch.Tensor, weights: torch.Tensor, shared_y, out: torch.Tensor) -> torch.Tensor:
+    """out[t] = sum_k weights[t, k] * y[where[t * top + k]] (+ shared_y[t]), in 32-bit in the order of k, one rounding."""
+    backend().combine_picks(y, where, weights, shared_y, out)
+    return out
+
+
 def attention_differential(y, q_col: int, out, out_col: int, out_scale: float, k_cache, v_cache, ctx, block_table, heads: int,
                            kv_heads: int, dim: int, v_dim: int, window, keep_first: int, scale: float, lam: float, sub_eps: float,
                            status=None):
@@ -689,6 +718,6 @@ def _counted(fn):
     return wrapper
 
 
-for _name in ("embedding", "logits_scale_cap", "rmsnorm", "layernorm", "polynorm", "scale_into", "head_norm_gate", "gla_scan", "delta_scan", "retention_scan", "route_experts", "attention_differential",
+for _name in ("embedding", "logits_scale_cap", "rmsnorm", "layernorm", "polynorm", "scale_into", "head_norm_gate", "gla_scan", "delta_scan", "retention_scan", "route_experts", "attention_differential", "route_topk", "expert_lists", "gather_picks", "combine_picks",
               "attention_prepare", "attention_general", "silu_mul", "rope_store", "linear", "paged_attention", "argmax", "sample"):  # the others count where they launch
     globals()[_name] = _counted(globals()[_name])

@@ -101,8 +101,13 @@ class Experts(FeedForward):
     weights and multiplies the chosen experts' columns by them (zero for the others); the down matrices are packed
     along the inner dimension, so the weighted sum over the experts and the shared expert is ONE product.  A step of a
     few tokens reads every expert's weights anyway; a long portion pays experts / top times the products' work for
-    two launches instead of two for every expert and no regrouping of the tokens.  Inner sizes that are no multiple
-    of 8 are zero-padded."""
+    two launches instead of two for every expert and no regrouping of the tokens.  So a step with many picks (tokens times
+    top, ``ops.EXPERTS_GROUPED_MIN_PICKS``) that is no step of single tokens groups its tokens by expert instead: the
+    picks of every token, the list of every expert's picks in rising order, the input rows sorted by expert, the two
+    products of every expert over its slice of rows (the host reads the experts' counts for that: one wait a layer),
+    the shared expert's two products over all rows, and one kernel that adds a token's picks with their weights in the
+    order of the picks, in 32-bit.  Inner sizes that are no multiple of 8 are zero-padded.  The down matrices are kept
+    twice (packed along the inner dimension for the one product, one by one for the grouped products)."""
 
     graph_safe = True
 
@@ -143,6 +148,12 @@ class Experts(FeedForward):
             gate_up, down = [m.float() for m in gate_up], [m.float() for m in down]
         self.w_gate_up = torch.cat(gate_up, dim=0).contiguous()
         self.w_down = torch.cat(down, dim=1).contiguous()
+        # for the grouped products: every expert's matrices as contiguous [n, k] (views of the packed rows; the down
+        # matrices as they were)
+        rows = [g.shape[0] for g in gate_up]
+        starts = [sum(rows[:i]) for i in range(len(rows))]
+        self.gate_up_of = [self.w_gate_up[a:a + n] for a, n in zip(starts, rows)]
+        self.down_of = [d.contiguous() for d in down]
 
     def weight_bytes(self) -> int:
         return sum(m.numel() * m.element_size() for m in (self.router, self.w_gate_up, self.w_down))
@@ -155,7 +166,39 @@ class Experts(FeedForward):
         T = h.shape[0]
         logits = torch.empty((T, s.experts), dtype=torch.float32, device=h.device)
         ops.linear(h, self.router, None, logits)
+        if ctx.max_q_len > 1 and T * s.top >= ops.EXPERTS_GROUPED_MIN_PICKS:
+            return self.grouped(h, logits)
         act = torch.empty((T, self.w_down.shape[1]), dtype=h.dtype, device=h.device)
         ops.linear_silu_mul(h, self.w_gate_up, act, then=ops.product_hint(self.w_down, "stream"))
         ops.route_experts(logits, s.top, act, self.inter)
         return ops.linear_to_stream(act, self.w_down, None, then=self.then)
+
+    def grouped(self, h, logits):
+        """The tokens grouped by expert (see the class)."""
+        s, ops, dev = self.spec, self.rt.ops, h.device
+        T, picks = h.shape[0], h.shape[0] * s.top
+        ids = torch.empty((T, s.top), dtype=torch.int32, device=dev)
+        weights = torch.empty((T, s.top), dtype=torch.float32, device=dev)
+        ops.route_topk(logits, s.top, ids, weights)
+        lists = torch.empty((s.experts, T), dtype=torch.int32, device=dev)
+        counts = torch.empty((s.experts,), dtype=torch.int32, device=dev)
+        ops.expert_lists(ids, lists, counts)
+        rows = torch.empty((picks, s.hidden), dtype=h.dtype, device=dev)
+        where = torch.empty((picks,), dtype=torch.int32, device=dev)
+        ops.gather_picks(h, lists, counts, s.top, rows, where)
+        shared_y = None
+        if s.shared_inter:          # the shared expert's products are enqueued before the host waits for the counts
+            act = torch.empty((T, self.down_of[-1].shape[1]), dtype=h.dtype, device=dev)
+            ops.linear_silu_mul(h, self.gate_up_of[-1], act)
+            shared_y = torch.empty((T, s.hidden), dtype=h.dtype, device=dev)
+            ops.linear(act, self.down_of[-1], None, shared_y)
+        act = torch.empty((picks, self.inter), dtype=h.dtype, device=dev)
+        y = torch.empty((picks, s.hidden), dtype=h.dtype, device=dev)
+        at = 0
+        for e, n in enumerate(counts.tolist()):
+            if n:
+                ops.linear_silu_mul(rows[at:at + n], self.gate_up_of[e], act[at:at + n])
+                ops.linear(act[at:at + n], self.down_of[e], None, y[at:at + n])
+            at += n
+        out = torch.empty((T, s.hidden), dtype=h.dtype, device=dev)
+        return ops.combine_picks(y, where, weights, shared_y, out)
