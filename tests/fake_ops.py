@@ -324,7 +324,9 @@ def retention_scan(y, q_col, k_col, v_col, decay, k_scale, frequencies, position
         state[row] = S
 
 
-def route_experts(logits, top, act, inter):
+def route_experts(logits, top, act, inter, x=None, router=None):
+    if logits is None:
+        logits = x.float() @ router.float().t()
     T, n = logits.shape
     w = torch.zeros((T, n), dtype=torch.float32)
     for t in range(T):
@@ -334,7 +336,9 @@ def route_experts(logits, top, act, inter):
     act[:, :n * inter] = torch.where(w[:, :, None] > 0, scaled, torch.zeros_like(scaled)).reshape(T, n * inter).to(act.dtype)
 
 
-def route_topk(logits, top, ids, weights):
+def route_topk(logits, top, ids, weights, x=None, router=None):
+    if logits is None:
+        logits = x.float() @ router.float().t()
     for t in range(logits.shape[0]):
         order = sorted(range(logits.shape[1]), key=lambda e: (-float(logits[t, e]), e))[:top]
         ids[t] = torch.tensor(order, dtype=torch.int32)

@@ -338,14 +338,41 @@ void retention_scan(const Tensor& y, int64_t q_col, int64_t k_col, int64_t v_col
                                             v_dim, (int)most_threads, status_ptr(status), stream_of(y)), "retention_scan");
 }
 
-void route_topk(const Tensor& logits, int64_t top, Tensor& ids, Tensor& weights) {
-    check_f32(logits, "logits"); check_i32(ids, "ids"); check_f32(weights, "weights");
-    TORCH_CHECK(logits.dim() == 2 && ids.dim() == 2 && ids.size(0) == logits.size(0) && ids.size(1) == top && weights.sizes() == ids.sizes(),
-                "route_topk: logits [tokens, experts], ids and weights [tokens, top]");
-    TORCH_CHECK(logits.size(1) <= 1024 && top >= 1 && top <= logits.size(1), "route_topk: 1 <= top <= experts <= 1024");
-    c10::cuda::CUDAGuard guard(logits.device());
-    check_launch(vtb::launch_route_topk(logits.data_ptr<float>(), logits.size(0), logits.size(1), top, ids.data_ptr<int>(),
-                                        weights.data_ptr<float>(), stream_of(logits)), "route_topk");
+// the router's logits as a tensor [tokens, experts], or the token's input x [tokens, width] and the router's matrix
+// [experts, width] (float32) from which the kernel forms them
+struct RouterInput {
+    const float* logits = nullptr;
+    const void* x = nullptr;
+    const float* router = nullptr;
+    int width = 0, tokens = 0, experts = 0, x_dtype = vtb::kF32;
+};
+
+RouterInput router_input(const c10::optional<Tensor>& logits, const c10::optional<Tensor>& x, const c10::optional<Tensor>& router, const char* who) {
+    RouterInput r;
+    if (logits.has_value()) {
+        check_f32(*logits, "logits");
+        TORCH_CHECK(logits->dim() == 2, who, ": logits [tokens, experts]");
+        r.logits = logits->data_ptr<float>(); r.tokens = logits->size(0); r.experts = logits->size(1);
+        return r;
+    }
+    TORCH_CHECK(x.has_value() && router.has_value(), who, ": logits, or the input rows and the router's matrix");
+    check_cuda(*x, "x"); check_f32(*router, "router");
+    TORCH_CHECK(x->dim() == 2 && router->dim() == 2 && router->size(1) == x->size(1) && x->size(1) % 8 == 0, who,
+                ": x [tokens, width], router [experts, width], width a multiple of 8");
+    r.x = x->data_ptr(); r.router = router->data_ptr<float>(); r.width = x->size(1); r.tokens = x->size(0); r.experts = router->size(0);
+    r.x_dtype = dtype_code(*x, "x");
+    return r;
+}
+
+void route_topk(c10::optional<Tensor> logits, int64_t top, Tensor& ids, Tensor& weights, c10::optional<Tensor> x, c10::optional<Tensor> router) {
+    check_i32(ids, "ids"); check_f32(weights, "weights");
+    const RouterInput r = router_input(logits, x, router, "route_topk");
+    TORCH_CHECK(ids.dim() == 2 && ids.size(0) == r.tokens && ids.size(1) == top && weights.sizes() == ids.sizes(),
+                "route_topk: ids and weights [tokens, top]");
+    TORCH_CHECK(r.experts <= 1024 && top >= 1 && top <= r.experts, "route_topk: 1 <= top <= experts <= 1024");
+    c10::cuda::CUDAGuard guard(ids.device());
+    check_launch(vtb::launch_route_topk(r.x_dtype, r.logits, r.x, r.router, r.width, r.tokens, r.experts, top, ids.data_ptr<int>(),
+                                        weights.data_ptr<float>(), stream_of(ids)), "route_topk");
 }
 
 void expert_lists(const Tensor& ids, Tensor& lists, Tensor& counts) {
@@ -384,14 +411,15 @@ void combine_picks(const Tensor& y, const Tensor& where, const Tensor& weights, 
                                            weights.size(1), out.size(0), sp, out.data_ptr(), stream_of(y)), "combine_picks");
 }
 
-void route_experts(const Tensor& logits, int64_t top, Tensor& act, int64_t inter) {
-    check_f32(logits, "logits"); check_cuda(act, "act");
-    TORCH_CHECK(logits.dim() == 2 && act.dim() == 2 && act.size(0) == logits.size(0), "route_experts: logits [tokens, experts], act [tokens, .]");
-    const int experts = logits.size(1);
-    TORCH_CHECK(experts >= 1 && experts <= 1024 && top >= 1 && top <= experts, "route_experts: 1 <= top <= experts <= 1024");
-    TORCH_CHECK(inter >= 0 && experts * inter <= act.size(1), "route_experts: experts * inter columns lie outside act");
+void route_experts(c10::optional<Tensor> logits, int64_t top, Tensor& act, int64_t inter, c10::optional<Tensor> x, c10::optional<Tensor> router) {
+    check_cuda(act, "act");
+    const RouterInput r = router_input(logits, x, router, "route_experts");
+    TORCH_CHECK(act.dim() == 2 && act.size(0) == r.tokens, "route_experts: act [tokens, .]");
+    TORCH_CHECK(r.x == nullptr || r.x_dtype == dtype_code(act, "act"), "route_experts: x and act of one dtype");
+    TORCH_CHECK(r.experts >= 1 && r.experts <= 1024 && top >= 1 && top <= r.experts, "route_experts: 1 <= top <= experts <= 1024");
+    TORCH_CHECK(inter >= 0 && r.experts * inter <= act.size(1), "route_experts: experts * inter columns lie outside act");
     c10::cuda::CUDAGuard guard(act.device());
-    check_launch(vtb::launch_route_experts(dtype_code(act, "act"), logits.data_ptr<float>(), logits.size(0), experts, top, act.data_ptr(),
+    check_launch(vtb::launch_route_experts(dtype_code(act, "act"), r.logits, r.x, r.router, r.width, r.tokens, r.experts, top, act.data_ptr(),
                                            act.size(1), inter, stream_of(act)), "route_experts");
 }
 
@@ -822,8 +850,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("attention_diff_supports", &vtb::attention_diff_supports);
     m.def("attention_diff_tile_rows", &vtb::attention_diff_tile_rows);
     m.def("retention_scan", &retention_scan);
-    m.def("route_experts", &route_experts);
-    m.def("route_topk", &route_topk);
+    m.def("route_experts", &route_experts, py::arg("logits"), py::arg("top"), py::arg("act"), py::arg("inter"), py::arg("x") = py::none(),
+          py::arg("router") = py::none());
+    m.def("route_topk", &route_topk, py::arg("logits"), py::arg("top"), py::arg("ids"), py::arg("weights"), py::arg("x") = py::none(),
+          py::arg("router") = py::none());
     m.def("expert_lists", &expert_lists);
     m.def("gather_picks", &gather_picks);
     m.def("combine_picks", &combine_picks);

@@ -58,9 +58,37 @@ __device__ __forceinline__ void pick_top(float* z, float* w, int* picked, float*
     }
 }
 
+// z[e] = logits[t, e], or, with the router's matrix [experts, width] (32-bit) and the token's input row x [width], the
+// dot product formed here in 32-bit: a warp an expert, a lane the same columns of every expert, the lanes' sums added by
+// the warp: the order depends on the width alone.
+template <typename T>
+__device__ __forceinline__ void router_logits(float* z, const float* __restrict__ logits, const T* __restrict__ x,
+                                              const float* __restrict__ router, int width, int experts, int t) {
+    if (x == nullptr) {
+        for (int e = threadIdx.x; e < experts; e += blockDim.x) z[e] = logits[(size_t)t * experts + e];
+        return;
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    const T* xr = x + (size_t)t * width;
+    for (int e = warp; e < experts; e += warps) {
+        const float* rr = router + (size_t)e * width;
+        float acc = 0.f;
+        for (int c = lane * 8; c < width; c += 256) {
+            float a[8], b[8];
+            Vec8<T>::load(xr + c, a);
+            Vec8<float>::load(rr + c, b);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc = fmaf(a[j], b[j], acc);
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) z[e] = acc;
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kRouteThreads)
-route_experts_kernel(const float* __restrict__ logits, int experts, int top, T* __restrict__ act, int act_stride, int inter) {
+route_experts_kernel(const float* __restrict__ logits, const T* __restrict__ x, const float* __restrict__ router, int width,
+                     int experts, int top, T* __restrict__ act, int act_stride, int inter) {
     __shared__ float z[kMaxExperts];          // the logits; a picked one is taken out
     __shared__ float w[kMaxExperts];          // the experts' weights, zero for those not picked
     __shared__ float picked_z[kMaxExperts];
@@ -68,10 +96,8 @@ route_experts_kernel(const float* __restrict__ logits, int experts, int top, T* 
     pdl_launch();
     pdl_wait();
     const int t = blockIdx.x;
-    for (int e = threadIdx.x; e < experts; e += blockDim.x) {
-        z[e] = logits[(size_t)t * experts + e];
-        w[e] = 0.f;
-    }
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) w[e] = 0.f;
+    router_logits(z, logits, x, router, width, experts, t);
     __syncthreads();
     pick_top(z, w, picked, picked_z, experts, top);
     __syncthreads();
@@ -100,18 +126,20 @@ route_experts_kernel(const float* __restrict__ logits, int experts, int top, T* 
 }
 
 // The picks themselves: ids[t, k] and weights[t, k] in falling order of the logits (for the grouped products).
-__global__ void __launch_bounds__(32)
-route_topk_kernel(const float* __restrict__ logits, int experts, int top, int* __restrict__ ids, float* __restrict__ weights) {
+template <typename T>
+__global__ void __launch_bounds__(kRouteThreads)
+route_topk_kernel(const float* __restrict__ logits, const T* __restrict__ x, const float* __restrict__ router, int width, int experts,
+                  int top, int* __restrict__ ids, float* __restrict__ weights) {
     __shared__ float z[kMaxExperts];
     __shared__ float picked_z[kMaxExperts];
     __shared__ int picked[kMaxExperts];
     pdl_launch();
     pdl_wait();
     const int t = blockIdx.x;
-    for (int e = threadIdx.x; e < experts; e += blockDim.x) z[e] = logits[(size_t)t * experts + e];
-    __syncwarp();
+    router_logits(z, logits, x, router, width, experts, t);
+    __syncthreads();
     pick_top(z, nullptr, picked, picked_z, experts, top);
-    __syncwarp();
+    __syncthreads();
     for (int k = threadIdx.x; k < top; k += blockDim.x) {
         ids[(size_t)t * top + k] = picked[k];
         weights[(size_t)t * top + k] = picked_z[k];
@@ -202,10 +230,15 @@ combine_picks_kernel(const T* __restrict__ y, int width, const int* __restrict__
     }
 }
 
-cudaError_t launch_route_topk(const float* logits, int n_tokens, int experts, int top, int* ids, float* weights, cudaStream_t stream) {
+cudaError_t launch_route_topk(int x_dtype, const float* logits, const void* x, const float* router, int width, int n_tokens, int experts,
+                              int top, int* ids, float* weights, cudaStream_t stream) {
     if (n_tokens == 0) return cudaSuccess;
-    if (experts < 1 || experts > kMaxExperts || top < 1 || top > experts) return cudaErrorInvalidValue;
-    return launch(route_topk_kernel, n_tokens, 32, 0, stream, logits, experts, top, ids, weights);
+    if (experts < 1 || experts > kMaxExperts || top < 1 || top > experts || (x != nullptr && width % 8)) return cudaErrorInvalidValue;
+    if (x_dtype == kBF16)
+        return launch(route_topk_kernel<__nv_bfloat16>, n_tokens, kRouteThreads, 0, stream, logits, (const __nv_bfloat16*)x, router, width,
+                      experts, top, ids, weights);
+    return launch(route_topk_kernel<float>, n_tokens, kRouteThreads, 0, stream, logits, (const float*)x, router, width, experts, top, ids,
+                  weights);
 }
 
 cudaError_t launch_expert_lists(const int* ids, int n_picks, int experts, int list_stride, int* lists, int* counts, cudaStream_t stream) {
@@ -235,14 +268,15 @@ cudaError_t launch_combine_picks(int dtype, const void* y, int width, const int*
                   (const float*)shared_y, (float*)out);
 }
 
-cudaError_t launch_route_experts(int dtype, const float* logits, int n_tokens, int experts, int top, void* act, int act_stride,
-                                 int inter, cudaStream_t stream) {
+cudaError_t launch_route_experts(int dtype, const float* logits, const void* x, const float* router, int width, int n_tokens, int experts,
+                                 int top, void* act, int act_stride, int inter, cudaStream_t stream) {
     if (n_tokens == 0) return cudaSuccess;
-    if (experts < 1 || experts > kMaxExperts || top < 1 || top > experts) return cudaErrorInvalidValue;
+    if (experts < 1 || experts > kMaxExperts || top < 1 || top > experts || (x != nullptr && width % 8)) return cudaErrorInvalidValue;
     if (dtype == kBF16)
-        return launch(route_experts_kernel<__nv_bfloat16>, n_tokens, kRouteThreads, 0, stream, logits, experts, top,
-                      (__nv_bfloat16*)act, act_stride, inter);
-    return launch(route_experts_kernel<float>, n_tokens, kRouteThreads, 0, stream, logits, experts, top, (float*)act, act_stride, inter);
+        return launch(route_experts_kernel<__nv_bfloat16>, n_tokens, kRouteThreads, 0, stream, logits, (const __nv_bfloat16*)x, router, width,
+                      experts, top, (__nv_bfloat16*)act, act_stride, inter);
+    return launch(route_experts_kernel<float>, n_tokens, kRouteThreads, 0, stream, logits, (const float*)x, router, width, experts, top,
+                  (float*)act, act_stride, inter);
 }
 
 }  // namespace vtb

@@ -99,12 +99,15 @@ cudaError_t launch_retention_scan(int dtype, const void* y, int stride, int q_co
 // Mixture of experts (experts.cu): for each row of logits [n_tokens, experts] the `top` largest choose the experts, the
 // softmax over the chosen logits weighs them; act[t, e * inter + i] *= weight of e (0 where e was not chosen), for
 // act [n_tokens, act_stride] of `dtype`.
-cudaError_t launch_route_experts(int dtype, const float* logits, int n_tokens, int experts, int top, void* act, int act_stride,
-                                 int inter, cudaStream_t stream);
+// The logits are given, or (x not null) formed in the kernel: logits[t, e] = x[t, :] . router[e, :] in 32-bit, x of `dtype`
+// [n_tokens, width], router float [experts, width].
+cudaError_t launch_route_experts(int dtype, const float* logits, const void* x, const float* router, int width, int n_tokens, int experts,
+                                 int top, void* act, int act_stride, int inter, cudaStream_t stream);
 // The grouped form: ids / weights [n_tokens, top] of each token's picks; lists [experts, list_stride] of the picks (flat
 // index t * top + k) of every expert in rising order and counts [experts]; sorted [n_picks, width] the input rows by
 // expert and where [n_picks] each pick's row; out[t] = sum_k weights[t, k] * y[where[t * top + k]] (+ shared_y[t]).
-cudaError_t launch_route_topk(const float* logits, int n_tokens, int experts, int top, int* ids, float* weights, cudaStream_t stream);
+cudaError_t launch_route_topk(int x_dtype, const float* logits, const void* x, const float* router, int width, int n_tokens, int experts,
+                              int top, int* ids, float* weights, cudaStream_t stream);
 cudaError_t launch_expert_lists(const int* ids, int n_picks, int experts, int list_stride, int* lists, int* counts, cudaStream_t stream);
 cudaError_t launch_gather_picks(int dtype, const void* x, int width, const int* lists, int list_stride, const int* counts, int experts,
                                 int top, int n_picks, void* sorted, int* where, cudaStream_t stream);

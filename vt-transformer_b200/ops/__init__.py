@@ -228,10 +228,12 @@ def attention_general(y, q_col: int, out, out_col: int, out_scale: float, k_cach
 EXPERTS_GROUPED_MIN_PICKS = int(os.environ.get("VTB200_EXPERTS_GROUPED_MIN_PICKS", "1024"))
 
 
-def route_topk(logits: torch.Tensor, top: int, ids: torch.Tensor, weights: torch.Tensor) -> None:
+def route_topk(logits, top: int, ids: torch.Tensor, weights: torch.Tensor, x=None, router=None) -> None:
     """ids[t, k] and weights[t, k]: the ``top`` largest router logits of every token in falling order (the lower index
-    among equals) and the softmax over them."""
-    backend().route_topk(logits, int(top), ids, weights)
+    among equals) and the softmax over them.  ``logits`` [tokens, experts] float32, or None with the tokens' input rows
+    ``x`` [tokens, width] and the router's matrix ``router`` [experts, width] (float32), from which the kernel forms
+    them as 32-bit dot products."""
+    backend().route_topk(logits, int(top), ids, weights, x, router)
 
 
 def expert_lists(ids: torch.Tensor, lists: torch.Tensor, counts: torch.Tensor) -> None:
@@ -274,12 +276,13 @@ def attention_differential(y, q_col: int, out, out_col: int, out_scale: float, k
                                          sub_eps=sub_eps)
 
 
-def route_experts(logits: torch.Tensor, top: int, act: torch.Tensor, inter: int) -> torch.Tensor:
+def route_experts(logits, top: int, act: torch.Tensor, inter: int, x=None, router=None) -> torch.Tensor:
     """For every token (row): the ``top`` largest of its router logits [experts] (float32; the lower index among
     equals) choose its experts, the softmax over the chosen logits weighs them; columns [e * inter, (e + 1) * inter) of
     ``act`` (what expert e's last product multiplies) are multiplied by expert e's weight, and set to zero for an
-    expert that was not chosen.  Columns beyond experts * inter (an expert that every token uses) stay."""
-    backend().route_experts(logits, int(top), act, int(inter))
+    expert that was not chosen.  Columns beyond experts * inter (an expert that every token uses) stay.  ``logits`` may be
+    None with ``x`` and ``router`` given, as for ``route_topk``."""
+    backend().route_experts(logits, int(top), act, int(inter), x, router)
     return act
 
 

@@ -95,7 +95,8 @@ class PolyNormMLP(FeedForward):
 
 @register_part("feed_forward", "experts")
 class Experts(FeedForward):
-    """See ``ExpertsSpec``.  The router's logits are a 32-bit product (its matrix is kept in 32-bit).  All experts'
+    """See ``ExpertsSpec``.  The router's logits are 32-bit dot products formed inside the routing kernel (its matrix is
+    kept in 32-bit).  All experts'
     gate and up matrices, and the shared expert's, are one packed matrix, so silu(gate) * up of every expert for every
     token is ONE product with the activation in its epilogue; one kernel then picks each token's experts, forms their
     weights and multiplies the chosen experts' columns by them (zero for the others); the down matrices are packed
@@ -164,22 +165,20 @@ class Experts(FeedForward):
     def forward(self, h, ctx):
         s, ops = self.spec, self.rt.ops
         T = h.shape[0]
-        logits = torch.empty((T, s.experts), dtype=torch.float32, device=h.device)
-        ops.linear(h, self.router, None, logits)
         if ctx.max_q_len > 1 and T * s.top >= ops.EXPERTS_GROUPED_MIN_PICKS:
-            return self.grouped(h, logits)
+            return self.grouped(h)
         act = torch.empty((T, self.w_down.shape[1]), dtype=h.dtype, device=h.device)
         ops.linear_silu_mul(h, self.w_gate_up, act, then=ops.product_hint(self.w_down, "stream"))
-        ops.route_experts(logits, s.top, act, self.inter)
+        ops.route_experts(None, s.top, act, self.inter, x=h, router=self.router)     # the router's logits are formed there, in 32-bit
         return ops.linear_to_stream(act, self.w_down, None, then=self.then)
 
-    def grouped(self, h, logits):
+    def grouped(self, h):
         """The tokens grouped by expert (see the class)."""
         s, ops, dev = self.spec, self.rt.ops, h.device
         T, picks = h.shape[0], h.shape[0] * s.top
         ids = torch.empty((T, s.top), dtype=torch.int32, device=dev)
         weights = torch.empty((T, s.top), dtype=torch.float32, device=dev)
-        ops.route_topk(logits, s.top, ids, weights)
+        ops.route_topk(None, s.top, ids, weights, x=h, router=self.router)
         lists = torch.empty((s.experts, T), dtype=torch.int32, device=dev)
         counts = torch.empty((s.experts,), dtype=torch.int32, device=dev)
         ops.expert_lists(ids, lists, counts)
