@@ -298,8 +298,38 @@ def attention_general(y, q_col, out, out_col, out_scale, k_cache, v_cache, posit
             out[t, out_col + h * v_dim:out_col + (h + 1) * v_dim] = o.to(out.dtype)
 
 
+def _turned(x, frequencies, positions):
+    if frequencies is not None and frequencies.numel():
+        half = frequencies.numel()
+        ang = positions.float()[:, None] * frequencies.float()[None, :]
+        c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+        a, b = x[..., :half].clone(), x[..., half:2 * half].clone()
+        x[..., :half] = a * c - b * s
+        x[..., half:2 * half] = b * c + a * s
+    return x
+
+
+def retention_carry(state, ends, starts, seq_row, seq_first, seq_count, seg_len, decay, status=None):
+    for s in range(seq_row.numel()):
+        row, first, count = int(seq_row[s]), int(seq_first[s]), int(seq_count[s])
+        S = state[row].clone()
+        for j in range(first, first + count):
+            starts[j] = S
+            S = (decay ** int(seg_len[j]))[:, None, None] * S + ends[j]
+        state[row] = S
+
+
+def retention_fix(y, q_col, positions, frequencies, starts, tiles, decay, o):
+    heads, dim, v_dim = starts.shape[1:]
+    q = _turned(y[:, q_col:q_col + heads * dim].float().view(-1, heads, dim).clone(), frequencies, positions)
+    for seg, begin, n, t0 in tiles.tolist():
+        for t in range(begin, begin + n):
+            add = torch.einsum("hdv,hd->hv", starts[seg], q[t]) * (decay ** (t - t0 + 1))[:, None]
+            o[t] += add.reshape(-1)
+
+
 def retention_scan(y, q_col, k_col, v_col, decay, k_scale, frequencies, positions, state, cu_q, rows, o, heads, dim, v_dim,
-                   status=None, most_threads=0):
+                   status=None, most_threads=0, ends=None):
     yf = y.float()
     T = y.shape[0]
 
@@ -317,11 +347,14 @@ def retention_scan(y, q_col, k_col, v_col, decay, k_scale, frequencies, position
     k = turn(yf[:, k_col:k_col + heads * dim].view(T, heads, dim).clone()) * k_scale
     v = yf[:, v_col:v_col + heads * v_dim].view(T, heads, v_dim)
     for row, a, b in _sequences(cu_q, rows):
-        S = state[row].clone()
+        S = torch.zeros_like(state[0]) if row < 0 else state[row].clone()      # a later segment of a cut walk starts from zeros
         for t in range(a, b):
             S = decay[:, None, None] * S + k[t][:, :, None] * v[t][:, None, :]
             o[t] = torch.einsum("hdv,hd->hv", S, q[t]).reshape(-1)
-        state[row] = S
+        if row < 0:
+            ends[-row - 1] = S
+        else:
+            state[row] = S
 
 
 def route_experts(logits, top, act, inter, x=None, router=None):

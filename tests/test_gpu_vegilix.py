@@ -105,6 +105,36 @@ def test_cuts_equal_the_plain_implementation(vegilix_folders, name, family, dtyp
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("segments", [(8, 3), (16, 8), (33, 2)])
+def test_long_retention_walks_cut_into_segments(vegilix_folders, monkeypatch, segments, dtype):
+    """A sequence that brings many tokens has its retention walk cut into segments that run side by side (the later ones
+    from zeros; the states carried and the outputs completed afterwards): forced here for short sequences, with segment
+    lengths that are no multiples of the staged batches of 16 tokens or of the tiles of 32."""
+    from vt_transformer_b200 import ops
+    monkeypatch.setattr(ops, "RETENTION_SEGMENT_MIN", segments[0])
+    monkeypatch.setattr(ops, "RETENTION_SEGMENTS", segments[1])
+    for name in ("retention_alone", "wide", "mix"):
+        folder = vegilix_folders(name if name == "retention_alone" else cases.for_dtype(name, dtype))
+        for family in ("whole", "portions", "mixed"):
+            cases.replay(folder, cases.prompts_for(name), family, DEV, dtype, sizes=(40, 3, 70, 2, 150), alone=name == "retention_alone")
+
+
+def test_the_cut_walk_leaves_the_state_of_the_walk_in_one_piece(vegilix_folders, monkeypatch):
+    """A prompt of 300 tokens in one step, cut into 8 segments, then 20 tokens decoded from the state it left: the decoded
+    logits equal the plain ones (the carried state is the walk's), in 32-bit."""
+    from vt_transformer_b200 import ops
+    monkeypatch.setattr(ops, "RETENTION_SEGMENT_MIN", 32)
+    folder = vegilix_folders("retention_alone")
+    ids = cases.prompts_for("retention_alone", lengths=[320])[0]
+    runner = cases.runner_for(folder, DEV, "float32", num_pages=1, max_requests=1)
+    row = runner.admit()
+    got = cases.step_all(runner, row, ids, [300] + [1] * 20)
+    runner.release(row)
+    ref = _logits(folder, ids)
+    assert float((got - ref).abs().max()) <= cases.tol("float32", ref, alone=True)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", ["mix", "wide", "experts_alone"])
 def test_tokens_grouped_by_expert(vegilix_folders, monkeypatch, name, dtype):
     """Portions with many picks group their tokens by expert (the experts' products over slices of sorted rows) instead of

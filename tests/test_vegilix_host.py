@@ -109,6 +109,17 @@ def test_tokens_grouped_by_expert_equal_the_plain_implementation(fake_backend, v
         cases.replay(vegilix_folders(name), cases.prompts_for(name), "mixed", "cpu", "float32")
 
 
+def test_long_retention_walks_cut_into_segments(fake_backend, vegilix_folders, monkeypatch):
+    """Sequences of 16 tokens and more in a step have their walk cut into up to 3 segments (states carried between them,
+    the later segments' outputs completed): whole prompts, portions and mixed batches still equal the plain walk."""
+    from vt_transformer_b200 import ops
+    monkeypatch.setattr(ops, "RETENTION_SEGMENT_MIN", 8)
+    monkeypatch.setattr(ops, "RETENTION_SEGMENTS", 3)
+    for name in ("retention_alone", "mix"):
+        for family in ("whole", "portions", "mixed"):
+            cases.replay(vegilix_folders(name), cases.prompts_for(name), family, "cpu", "float32", sizes=(40, 3, 17, 2, 64))
+
+
 def test_a_span_repeated_from_the_first_layer(fake_backend, vegilix_folders):
     cases.replay(vegilix_folders("looped_start"), cases.prompts_for("looped_start"), "mixed", "cpu", "float32")
 

@@ -316,8 +316,17 @@ void attention_diff(const Tensor& y, int64_t q_col, Tensor& out, int64_t out_col
 
 void retention_scan(const Tensor& y, int64_t q_col, int64_t k_col, int64_t v_col, const Tensor& decay, double k_scale,
                     c10::optional<Tensor> frequencies, const Tensor& positions, Tensor& state, const Tensor& cu_q, const Tensor& rows,
-                    Tensor& o, int64_t heads, int64_t dim, int64_t v_dim, c10::optional<Tensor> status, int64_t most_threads) {
+                    Tensor& o, int64_t heads, int64_t dim, int64_t v_dim, c10::optional<Tensor> status, int64_t most_threads,
+                    c10::optional<Tensor> ends) {
     check_scan(y, state, cu_q, rows, o, heads, dim, v_dim, "retention_scan");
+    float* ep = nullptr;
+    int end_rows = 0;
+    if (ends.has_value()) {
+        check_f32(*ends, "ends");
+        TORCH_CHECK(ends->dim() == 4 && ends->size(1) == heads && ends->size(2) == dim && ends->size(3) == v_dim, "retention_scan: ends [n, heads, dim, v_dim]");
+        ep = ends->data_ptr<float>();
+        end_rows = ends->size(0);
+    }
     check_f32(decay, "decay"); check_i32(positions, "positions");
     TORCH_CHECK(decay.numel() == heads, "retention_scan: one decay for each head");
     TORCH_CHECK(positions.numel() == y.size(0), "retention_scan: one position a token");
@@ -335,7 +344,46 @@ void retention_scan(const Tensor& y, int64_t q_col, int64_t k_col, int64_t v_col
     check_launch(vtb::launch_retention_scan(dtype_code(y, "y"), y.data_ptr(), y.size(1), q_col, k_col, v_col, decay.data_ptr<float>(),
                                             (float)k_scale, fp, half, positions.data_ptr<int>(), state.data_ptr<float>(), state.size(0),
                                             cu_q.data_ptr<int>(), rows.data_ptr<int>(), rows.numel(), o.data_ptr<float>(), heads, dim,
-                                            v_dim, (int)most_threads, status_ptr(status), stream_of(y)), "retention_scan");
+                                            v_dim, (int)most_threads, status_ptr(status), ep, end_rows, stream_of(y)), "retention_scan");
+}
+
+void retention_carry(Tensor& state, const Tensor& ends, Tensor& starts, const Tensor& seq_row, const Tensor& seq_first,
+                     const Tensor& seq_count, const Tensor& seg_len, const Tensor& decay, c10::optional<Tensor> status) {
+    check_f32(state, "state"); check_f32(ends, "ends"); check_f32(starts, "starts"); check_f32(decay, "decay");
+    check_i32(seq_row, "seq_row"); check_i32(seq_first, "seq_first"); check_i32(seq_count, "seq_count"); check_i32(seg_len, "seg_len");
+    TORCH_CHECK(state.dim() == 4 && ends.dim() == 4 && starts.sizes() == ends.sizes() && ends.size(1) == state.size(1) &&
+                ends.size(2) == state.size(2) && ends.size(3) == state.size(3) && decay.numel() == state.size(1),
+                "retention_carry: state [rows, heads, dim, v_dim], ends and starts [n, heads, dim, v_dim], decay [heads]");
+    TORCH_CHECK(seq_first.numel() == seq_row.numel() && seq_count.numel() == seq_row.numel() && seg_len.numel() == ends.size(0),
+                "retention_carry: one row, first and count a split sequence; one length a later segment");
+    c10::cuda::CUDAGuard guard(state.device());
+    check_launch(vtb::launch_retention_carry(state.data_ptr<float>(), state.size(0), ends.data_ptr<float>(), starts.data_ptr<float>(),
+                                             seq_row.data_ptr<int>(), seq_first.data_ptr<int>(), seq_count.data_ptr<int>(),
+                                             seg_len.data_ptr<int>(), seq_row.numel(), decay.data_ptr<float>(), state.size(1), state.size(2),
+                                             state.size(3), status_ptr(status), stream_of(state)), "retention_carry");
+}
+
+void retention_fix(const Tensor& y, int64_t q_col, const Tensor& positions, c10::optional<Tensor> frequencies, const Tensor& starts,
+                   const Tensor& tiles, const Tensor& decay, Tensor& o) {
+    check_cuda(y, "y"); check_i32(positions, "positions"); check_f32(starts, "starts"); check_i32(tiles, "tiles"); check_f32(decay, "decay");
+    check_f32(o, "o");
+    TORCH_CHECK(starts.dim() == 4 && tiles.dim() == 2 && tiles.size(1) == 4, "retention_fix: starts [n, heads, dim, v_dim], tiles [m, 4]");
+    const int heads = starts.size(1), dim = starts.size(2), v_dim = starts.size(3);
+    TORCH_CHECK(y.dim() == 2 && o.dim() == 2 && o.size(0) == y.size(0) && o.size(1) == heads * v_dim && decay.numel() == heads &&
+                positions.numel() == y.size(0), "retention_fix: o [tokens, heads * v_dim], one position a token, one decay a head");
+    check_cols(y, q_col, heads * dim, "retention_fix (q)");
+    const float* fp = nullptr;
+    int half = 0;
+    if (frequencies.has_value()) {
+        check_f32(*frequencies, "frequencies");
+        fp = frequencies->data_ptr<float>();
+        half = frequencies->numel();
+        TORCH_CHECK(2 * half <= dim, "retention_fix: the rotation covers more than the head");
+    }
+    c10::cuda::CUDAGuard guard(y.device());
+    check_launch(vtb::launch_retention_fix(dtype_code(y, "y"), y.data_ptr(), y.size(1), q_col, positions.data_ptr<int>(), fp, half,
+                                           starts.data_ptr<float>(), tiles.data_ptr<int>(), tiles.size(0), decay.data_ptr<float>(),
+                                           o.data_ptr<float>(), heads, dim, v_dim, stream_of(y)), "retention_fix");
 }
 
 // the router's logits as a tensor [tokens, experts], or the token's input x [tokens, width] and the router's matrix
@@ -849,7 +897,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("attention_diff", &attention_diff);
     m.def("attention_diff_supports", &vtb::attention_diff_supports);
     m.def("attention_diff_tile_rows", &vtb::attention_diff_tile_rows);
-    m.def("retention_scan", &retention_scan);
+    m.def("retention_scan", &retention_scan, py::arg("y"), py::arg("q_col"), py::arg("k_col"), py::arg("v_col"), py::arg("decay"),
+          py::arg("k_scale"), py::arg("frequencies"), py::arg("positions"), py::arg("state"), py::arg("cu_q"), py::arg("rows"), py::arg("o"),
+          py::arg("heads"), py::arg("dim"), py::arg("v_dim"), py::arg("status") = py::none(), py::arg("most_threads") = 0,
+          py::arg("ends") = py::none());
+    m.def("retention_carry", &retention_carry);
+    m.def("retention_fix", &retention_fix);
     m.def("route_experts", &route_experts, py::arg("logits"), py::arg("top"), py::arg("act"), py::arg("inter"), py::arg("x") = py::none(),
           py::arg("router") = py::none());
     m.def("route_topk", &route_topk, py::arg("logits"), py::arg("top"), py::arg("ids"), py::arg("weights"), py::arg("x") = py::none(),

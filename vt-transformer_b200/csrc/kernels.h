@@ -94,7 +94,17 @@ cudaError_t launch_attention_diff(const void* y, int y_stride, int q_col, void* 
 cudaError_t launch_retention_scan(int dtype, const void* y, int stride, int q_col, int k_col, int v_col, const float* decay,
                                   float k_scale, const float* freq, int half, const int* positions, float* state, int state_rows,
                                   const int* cu_q, const int* rows, int n_seqs, float* out, int heads, int dim, int v_dim,
-                                  int most_threads, int* status, cudaStream_t stream);
+                                  int most_threads, int* status, float* ends, int end_rows, cudaStream_t stream);
+// A long walk cut into segments (see recurrent.cu): rows[i] = -(n + 1) above starts segment i from zeros and leaves its
+// last state in ends[n].  Carry: for split sequence s with later segments first .. first + count - 1 of lengths seg_len:
+// starts[n] = the state before later segment n, and the request's row gets the last state.  Fix: tiles (later segment,
+// first token, tokens <= 32, the segment's first token): out[t] += decay^(t - t0 + 1) starts[n]^T q_t.
+cudaError_t launch_retention_carry(float* state, int state_rows, const float* ends, float* starts, const int* seq_row,
+                                   const int* seq_first, const int* seq_count, const int* seg_len, int n_split, const float* decay,
+                                   int heads, int dim, int v_dim, int* status, cudaStream_t stream);
+cudaError_t launch_retention_fix(int dtype, const void* y, int stride, int q_col, const int* positions, const float* freq, int half,
+                                 const float* starts, const int* tiles, int n_tiles, const float* decay, float* out, int heads, int dim,
+                                 int v_dim, cudaStream_t stream);
 
 // Mixture of experts (experts.cu): for each row of logits [n_tokens, experts] the `top` largest choose the experts, the
 // softmax over the chosen logits weighs them; act[t, e * inter + i] *= weight of e (0 where e was not chosen), for

@@ -53,6 +53,10 @@ struct ScanArgs {
     const float* freq;            // [half]: pairs (i, i + half) of a head's q and k turn by positions[t] * freq[i]
     int half;
     const int* positions;         // [tokens]
+    // retention, a long walk cut into segments that run side by side: a "sequence" whose row is -(n + 1) starts from a
+    // state of zeros and leaves its last state in ends[n] instead of a request's row
+    float* ends;                  // [end rows, heads, dim, v_dim]
+    int end_rows;
 };
 
 __device__ __forceinline__ float log_sigmoid(float z) {
@@ -71,7 +75,7 @@ __device__ __forceinline__ float sigmoid(float z) { return 1.f / (1.f + expf(-z)
 // Fixed: retention.  No gate: the decay is one number a head, k (not q) carries the scale, and the staged q and k are
 // rotated in 32-bit where they lie in shared memory.
 template <typename T, int KD, bool Delta, bool Walk, bool Fixed>
-__global__ void __launch_bounds__(Walk ? 256 : scan_threads(KD), 1)
+__global__ void __launch_bounds__(Walk ? 256 : scan_threads(KD), (Walk && Fixed && KD <= 16) ? 3 : 1)
 scan_kernel(const ScanArgs a) {
     extern __shared__ __align__(16) float smem[];
     pdl_launch();
@@ -105,7 +109,8 @@ scan_kernel(const ScanArgs a) {
     const int t0 = a.cu_q[seq], t1 = a.cu_q[seq + 1];
     if (t1 <= t0) return;                                   // a sequence without tokens in this step (padding): its state stays
     const int row = a.rows[seq];
-    if (row < 0 || row >= a.state_rows) {
+    const bool later = Fixed && row < 0 && a.ends != nullptr;      // a later segment of a walk that was cut
+    if (later ? (-row - 1 >= a.end_rows) : (row < 0 || row >= a.state_rows)) {
         if (tid == 0) set_status(a.status, kStatusBadRow, row);
         return;
     }
@@ -167,12 +172,13 @@ scan_kernel(const ScanArgs a) {
         if (col0 + r < v_dim) from_col[k] = a.v_col + h * v_dim + col0 + r;
     }
 
-    float* sp = a.state + (((size_t)row * a.heads + h) * dim) * v_dim;
+    float* sp = later ? a.ends + (((size_t)(-row - 1) * a.heads + h) * dim) * v_dim
+                      : a.state + (((size_t)row * a.heads + h) * dim) * v_dim;
     float S[KD];
 #pragma unroll
     for (int i = 0; i < KD; ++i) {
         const int r = g * KD + i;
-        S[i] = (col_ok && r < dim) ? sp[(size_t)r * v_dim + j] : 0.f;
+        S[i] = (col_ok && r < dim && !later) ? sp[(size_t)r * v_dim + j] : 0.f;
     }
     int meet = 0;
     for (int tb0 = t0; tb0 < t1; tb0 += TB) {
@@ -398,14 +404,138 @@ cudaError_t launch_delta_scan(int dtype, const void* y, int stride, int r_col, i
 cudaError_t launch_retention_scan(int dtype, const void* y, int stride, int q_col, int k_col, int v_col, const float* decay,
                                   float k_scale, const float* freq, int half, const int* positions, float* state, int state_rows,
                                   const int* cu_q, const int* rows, int n_seqs, float* out, int heads, int dim, int v_dim,
-                                  int most_threads, int* status, cudaStream_t stream) {
+                                  int most_threads, int* status, float* ends, int end_rows, cudaStream_t stream) {
     if (n_seqs == 0) return cudaSuccess;
     if (2 * half > dim) return cudaErrorInvalidValue;
     // no low-rank gate (rank 0); the gate's bias slot carries the heads' decays, c2 the scale of k
     ScanArgs a = {y, stride, q_col, k_col, v_col, 0, 0, 0, nullptr, decay, nullptr, 0.f, k_scale, state, state_rows, cu_q, rows,
-                  out, heads, dim, v_dim, 1, 1, most_threads, status, freq, half, positions};
+                  out, heads, dim, v_dim, 1, 1, most_threads, status, freq, half, positions, ends, end_rows};
     return dtype == kBF16 ? launch_scan_t<__nv_bfloat16, false, true>(a, n_seqs, stream)
                           : launch_scan_t<float, false, true>(a, n_seqs, stream);
+}
+
+// ------------------------------------------------------------------------- retention: a long walk cut into segments
+//
+// With one fixed decay a head the recurrence is linear in the state it starts from: a segment that starts from zeros
+// gives each of its tokens the share of the segment's own keys, and what the state before the segment adds to token t
+// is decay^(t - t0 + 1) S_before^T q_t.  So the segments of a long portion run side by side (the scan kernel, the
+// first segment from the request's state, the later ones from zeros into `ends`); one kernel then carries the state
+// from segment to segment (S_before of the next = decay^length S_before + end), leaving every later segment's
+// S_before in `starts` and the last state in the request's row; and one adds the missing share to the later segments'
+// outputs.  Everything in 32-bit; only the order of the sums differs from the walk in one piece.
+
+// One thread an element of a (sequence, head)'s state; the sequence's later segments in order.
+__global__ void __launch_bounds__(256)
+retention_carry_kernel(float* __restrict__ state, int state_rows, const float* __restrict__ ends, float* __restrict__ starts,
+                       const int* __restrict__ seq_row, const int* __restrict__ seq_first, const int* __restrict__ seq_count,
+                       const int* __restrict__ seg_len, const float* __restrict__ decay, int heads, int per_head, int* status) {
+    pdl_launch();
+    pdl_wait();
+    const int s = blockIdx.x, h = blockIdx.y;
+    const int e = blockIdx.z * blockDim.x + threadIdx.x;
+    if (e >= per_head) return;
+    const int row = seq_row[s];
+    if (row < 0 || row >= state_rows) {
+        if (e == 0) set_status(status, kStatusBadRow, row);
+        return;
+    }
+    const int first = seq_first[s], count = seq_count[s];
+    const float g = decay[h];
+    float* sp = state + ((size_t)row * heads + h) * per_head + e;
+    float S = *sp;                                              // the state after the first segment
+    for (int j = 0; j < count; ++j) {
+        const size_t at = ((size_t)(first + j) * heads + h) * per_head + e;
+        starts[at] = S;
+        S = fmaf(powf(g, (float)seg_len[first + j]), S, ends[at]);
+    }
+    *sp = S;
+}
+
+// A tile of up to 32 tokens of a later segment, 128 columns of a head: out[t, j] += decay^(t - t0 + 1) sum_i q_t[i] S[i, j],
+// q rotated as the scan rotates it.  The state's rows come 32 at a time into registers, the tokens' q into shared memory.
+template <typename T>
+__global__ void __launch_bounds__(128)
+retention_fix_kernel(const T* __restrict__ y, int stride, int q_col, const int* __restrict__ positions, const float* __restrict__ freq,
+                     int half, const float* __restrict__ starts, const int4* __restrict__ tiles, const float* __restrict__ decay,
+                     float* __restrict__ out, int heads, int dim, int v_dim) {
+    constexpr int TT = 32, RR = 32;
+    __shared__ __align__(16) float qs[TT][RR];
+    pdl_launch();
+    pdl_wait();
+    const int4 tile = tiles[blockIdx.x];            // (later segment, first token of the tile, tokens, first token of the segment)
+    const int seg = tile.x, t_begin = tile.y, n = tile.z, t0 = tile.w;
+    const int h = blockIdx.y, j = blockIdx.z * blockDim.x + threadIdx.x;
+    const bool col_ok = j < v_dim;
+    const float* S = starts + ((size_t)seg * heads + h) * dim * v_dim;
+    float acc[TT];
+#pragma unroll
+    for (int tk = 0; tk < TT; ++tk) acc[tk] = 0.f;
+    for (int r0 = 0; r0 < dim; r0 += RR) {
+        __syncthreads();
+        for (int e = threadIdx.x; e < TT * RR; e += blockDim.x) {
+            const int tk = e / RR, i = r0 + e % RR;
+            float v = 0.f;
+            if (tk < n && i < dim) {
+                const T* qp = y + (size_t)(t_begin + tk) * stride + q_col + h * dim;
+                v = to_float(qp[i]);
+                if (i < 2 * half) {
+                    const int f = i < half ? i : i - half;
+                    float sn, cs;
+                    sincosf((float)positions[t_begin + tk] * freq[f], &sn, &cs);
+                    v = i < half ? v * cs - to_float(qp[i + half]) * sn : v * cs + to_float(qp[i - half]) * sn;
+                }
+            }
+            qs[tk][e % RR] = v;
+        }
+        float Sr[RR];
+#pragma unroll
+        for (int i = 0; i < RR; ++i) Sr[i] = (col_ok && r0 + i < dim) ? S[(size_t)(r0 + i) * v_dim + j] : 0.f;
+        __syncthreads();
+#pragma unroll
+        for (int tk = 0; tk < TT; ++tk) {
+            const float4* q4 = reinterpret_cast<const float4*>(qs[tk]);
+            float part[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int i = 0; i < RR / 4; ++i) {
+                const float4 q = q4[i];
+                part[0] = fmaf(q.x, Sr[4 * i + 0], part[0]);
+                part[1] = fmaf(q.y, Sr[4 * i + 1], part[1]);
+                part[2] = fmaf(q.z, Sr[4 * i + 2], part[2]);
+                part[3] = fmaf(q.w, Sr[4 * i + 3], part[3]);
+            }
+            acc[tk] += (part[0] + part[1]) + (part[2] + part[3]);
+        }
+    }
+    if (!col_ok) return;
+    const float g = decay[h];
+#pragma unroll
+    for (int tk = 0; tk < TT; ++tk) {
+        if (tk >= n) break;
+        const int t = t_begin + tk;
+        float* o = out + (size_t)t * heads * v_dim + h * v_dim + j;
+        *o = fmaf(powf(g, (float)(t - t0 + 1)), acc[tk], *o);
+    }
+}
+
+cudaError_t launch_retention_carry(float* state, int state_rows, const float* ends, float* starts, const int* seq_row,
+                                   const int* seq_first, const int* seq_count, const int* seg_len, int n_split, const float* decay,
+                                   int heads, int dim, int v_dim, int* status, cudaStream_t stream) {
+    if (n_split == 0) return cudaSuccess;
+    const int per_head = dim * v_dim;
+    return launch(retention_carry_kernel, dim3(n_split, heads, (per_head + 255) / 256), 256, 0, stream, state, state_rows, ends, starts,
+                  seq_row, seq_first, seq_count, seg_len, decay, heads, per_head, status);
+}
+
+cudaError_t launch_retention_fix(int dtype, const void* y, int stride, int q_col, const int* positions, const float* freq, int half,
+                                 const float* starts, const int* tiles, int n_tiles, const float* decay, float* out, int heads, int dim,
+                                 int v_dim, cudaStream_t stream) {
+    if (n_tiles == 0) return cudaSuccess;
+    const dim3 grid(n_tiles, heads, (v_dim + 127) / 128);
+    if (dtype == kBF16)
+        return launch(retention_fix_kernel<__nv_bfloat16>, grid, 128, 0, stream, (const __nv_bfloat16*)y, stride, q_col, positions, freq,
+                      half, starts, reinterpret_cast<const int4*>(tiles), decay, out, heads, dim, v_dim);
+    return launch(retention_fix_kernel<float>, grid, 128, 0, stream, (const float*)y, stride, q_col, positions, freq, half, starts,
+                  reinterpret_cast<const int4*>(tiles), decay, out, heads, dim, v_dim);
 }
 
 // ------------------------------------------------------------------------- norm of each head's output, gate

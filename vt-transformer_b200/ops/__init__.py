@@ -177,6 +177,60 @@ def delta_scan(y, r_col: int, k_col: int, v_col: int, a_col: int, w1_col: int, w
     return o
 
 
+# A sequence that brings this many tokens in a step, twice over, has its retention walk cut into up to RETENTION_SEGMENTS
+# segments that run side by side (see ``retention_scan``).
+RETENTION_SEGMENT_MIN = int(os.environ.get("VTB200_RETENTION_SEGMENT_MIN", "128"))
+RETENTION_SEGMENTS = int(os.environ.get("VTB200_RETENTION_SEGMENTS", "8"))
+
+
+class _RetentionPlan:
+    """How a step's long walks are cut: the segments as the scan kernel's sequences (``cu``, ``rows``: a request's row
+    for a sequence's first segment, -(n + 1) for its later segment n), for every cut sequence its row, its first later
+    segment and their count, every later segment's length, and the tiles of up to 32 tokens of the later segments."""
+
+    def __init__(self, ctx, device):
+        import numpy as np
+        cu, rows, seq_row, seq_first, seq_count, seg_len, tiles = [], [], [], [], [], [], []
+        for s in ctx.seqs:
+            pieces = min(RETENTION_SEGMENTS, s.length // max(1, RETENTION_SEGMENT_MIN))
+            if pieces < 2:
+                cu.append(s.offset)
+                rows.append(s.row)
+                continue
+            size = -(-s.length // pieces)
+            seq_row.append(s.row)
+            seq_first.append(len(seg_len))
+            for a in range(0, s.length, size):
+                b = min(s.length, a + size)
+                cu.append(s.offset + a)
+                if a == 0:
+                    rows.append(s.row)
+                    continue
+                rows.append(-(len(seg_len) + 1))
+                tiles += [(len(seg_len), s.offset + t, min(32, b - t), s.offset + a) for t in range(a, b, 32)]
+                seg_len.append(b - a)
+            seq_count.append(len(seg_len) - seq_first[-1])
+        cu.append(ctx.n_tokens)
+        self.n_later = len(seg_len)
+        if not self.n_later:
+            return
+        parts = [cu, rows, seq_row, seq_first, seq_count, seg_len, [v for t in tiles for v in t]]
+        offs, total = [], 0
+        for p in parts:
+            offs.append(total)
+            total += (len(p) + 3) & ~3                       # every array starts on a 16-byte boundary
+        host = torch.zeros(total, dtype=torch.int32)
+        for o, p in zip(offs, parts):
+            host[o:o + len(p)] = torch.from_numpy(np.asarray(p, dtype=np.int32))
+        if torch.device(device).type == "cuda":
+            host = host.pin_memory()
+        buf = host.to(device, non_blocking=True)
+        seg = lambda i: buf[offs[i]:offs[i] + len(parts[i])]
+        self.cu, self.rows, self.seq_row, self.seq_first, self.seq_count, self.seg_len = (seg(i) for i in range(6))
+        self.tiles = seg(6).view(-1, 4)
+        self.n_segments = len(rows)
+
+
 def retention_scan(y, q_col: int, k_col: int, v_col: int, decay: torch.Tensor, k_scale: float, frequencies, state: torch.Tensor,
                    ctx, o: torch.Tensor, heads: int, dim: int, v_dim: int, status=None):
     """Retention over the step's tokens, sequence by sequence and head by head, in the order of the tokens:
@@ -184,9 +238,32 @@ def retention_scan(y, q_col: int, k_col: int, v_col: int, decay: torch.Tensor, k
     head of q and k were rotated, pairs (i, i + len), by position * frequencies[i] (a 32-bit product, in 32-bit;
     ``frequencies`` None: no rotation).  q, k and v are columns of ``y``; ``decay`` [heads] float32; ``state``
     [request rows, heads, dim, v_dim] (float32) is read at the step's ``ctx.rows`` and left as after the last token;
-    ``o`` [T, heads * v_dim] is float32.  Rotation, state and sums are 32-bit."""
-    backend().retention_scan(y, int(q_col), int(k_col), int(v_col), decay, float(k_scale), frequencies, ctx.positions, state,
-                             ctx.cu_q, ctx.rows, o, int(heads), int(dim), int(v_dim), status, _scan_threads(ctx))
+    ``o`` [T, heads * v_dim] is float32.  Rotation, state and sums are 32-bit.
+
+    A sequence that brings many tokens is cut into segments that run side by side: the recurrence is linear in the
+    state it starts from, so the later segments start from zeros, one kernel carries the state from segment to segment,
+    and one adds decay^(t - t0 + 1) S_before^T q_t to the later segments' tokens; 32-bit throughout, only the order of
+    the sums differs."""
+    be = backend()
+    plan = None
+    if ctx.seqs and ctx.max_q_len >= 2 * RETENTION_SEGMENT_MIN and RETENTION_SEGMENTS > 1:
+        key = ("retention_plan", RETENTION_SEGMENT_MIN, RETENTION_SEGMENTS)
+        plan = ctx.extras.get(key)
+        if plan is None:
+            plan = ctx.extras[key] = _RetentionPlan(ctx, y.device)
+    if plan is None or not plan.n_later:
+        be.retention_scan(y, int(q_col), int(k_col), int(v_col), decay, float(k_scale), frequencies, ctx.positions, state,
+                          ctx.cu_q, ctx.rows, o, int(heads), int(dim), int(v_dim), status, _scan_threads(ctx))
+        return o
+    ends = torch.empty((plan.n_later, heads, dim, v_dim), dtype=torch.float32, device=y.device)
+    starts = torch.empty_like(ends)
+    threads = SCAN_WALK_THREADS if ctx.n_tokens >= 16 * plan.n_segments else 0
+    be.retention_scan(y, int(q_col), int(k_col), int(v_col), decay, float(k_scale), frequencies, ctx.positions, state, plan.cu,
+                      plan.rows, o, int(heads), int(dim), int(v_dim), status, threads, ends)
+    global launches
+    launches += 2
+    be.retention_carry(state, ends, starts, plan.seq_row, plan.seq_first, plan.seq_count, plan.seg_len, decay, status)
+    be.retention_fix(y, int(q_col), ctx.positions, frequencies, starts, plan.tiles, decay, o)
     return o
 
 
