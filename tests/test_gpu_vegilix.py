@@ -159,6 +159,9 @@ def test_cuts_through_the_tensor_core_attention_kernel(vegilix_folders, family, 
     cases.replay(vegilix_folders("tensor"), cases.prompts_for("tensor"), family, DEV, "bfloat16", sizes=sizes, page_size=page_size, tail=70)
     if page_size == 16:
         cases.replay(vegilix_folders("tensor"), cases.prompts_for("tensor"), family, DEV, "float32", sizes=sizes, tail=70)
+    # heads of 128 with values of 256 and of 128, three query heads a head of values
+    assert ops.backend().attention_diff_supports(128, 256, 3, 1) and ops.backend().attention_diff_supports(128, 128, 2, 2)
+    cases.replay(vegilix_folders("tensor_wide"), cases.prompts_for("tensor_wide"), family, DEV, "bfloat16", sizes=sizes, page_size=page_size, tail=70)
 
 
 def test_the_windows_edge_and_the_kept_first_tokens_through_the_tensor_core_kernel(vegilix_folders, tmp_path):

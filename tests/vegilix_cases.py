@@ -68,13 +68,15 @@ CONFIGS: Dict[str, dict] = {
     "tensor": _model(200, 64, [_att(4, 2, 32, 64, 16, 1e4, 0.18, 0.3, 150, 5, scaling=(8.0, 1.0, 4.0, 128), mlp=_moe(3, 3, 24, 16)),
                                _att(2, 1, 64, 128, 64, 500.0, 0.125, 0.2, 40, 70), _ret(2, 16, 16, 16, 1e4, [0.9, 0.95]),
                                _att(2, 2, 64, 64, 32, 1e5, 0.125, 0.35, None, 0)], loop=(0, 2, 2), mult=0.8),
+    "tensor_wide": _model(160, 64, [_att(3, 1, 128, 256, 64, 1e4, 0.09, 0.3, 50, 2, mlp=_moe(2, 2, 16, None)),
+                                    _att(2, 2, 128, 128, 128, 300.0, 0.09, 0.15, None, 0)], mult=0.8),
     "tensor_alone": _model(128, 64, [_att(4, 2, 32, 64, 16, 1e4, 0.18, 0.3, 100, 3)], mult=0.9),
     "looped_start": _model(128, 48, [_att(2, 1, 16, 16, 16, 1e4, 0.25, 0.3, 18, 1, mlp=_moe(3, 2, 16, 16)),
                                      _ret(2, 16, 24, 16, 1e4, [0.9, 0.99], mlp=_moe(3, 2, 16, 16))], loop=(0, 1, 3), mult=0.7),
 }
-SIGMA = {"tensor": 0.15, "tensor_alone": 0.25, "mix": 0.15, "wide": 0.12, "attention_alone": 0.25, "retention_alone": 0.2, "experts_alone": 0.2, "looped_start": 0.2}
+SIGMA = {"tensor": 0.15, "tensor_wide": 0.12, "tensor_alone": 0.25, "mix": 0.15, "wide": 0.12, "attention_alone": 0.25, "retention_alone": 0.2, "experts_alone": 0.2, "looped_start": 0.2}
 SEED = {n: 300 + i for i, n in enumerate(CONFIGS)}
-LENGTHS = {"tensor": [1, 70, 150, 330, 260], "tensor_alone": [3, 130, 270], "mix": [1, 9, 40, 71, 130], "wide": [3, 33, 90, 152], "attention_alone": [2, 30, 77], "retention_alone": [1, 25, 66],
+LENGTHS = {"tensor": [1, 70, 150, 330, 260], "tensor_wide": [2, 90, 200], "tensor_alone": [3, 130, 270], "mix": [1, 9, 40, 71, 130], "wide": [3, 33, 90, 152], "attention_alone": [2, 30, 77], "retention_alone": [1, 25, 66],
            "experts_alone": [4, 19, 50], "looped_start": [5, 48, 97]}
 
 
