@@ -80,6 +80,28 @@ def test_routing_kernel(dtype, experts, top, inter):
         ref[t, :experts * inter] = (ref[t, :experts * inter].view(experts, inter) * w[:, None]).reshape(-1)
     assert float((got.double().cpu() - ref).abs().max()) <= (1e-5 if dtype == torch.float32 else 3e-2)
     assert torch.equal(got.cpu()[:, experts * inter:], act[:, experts * inter:])     # the shared expert's columns stay
+    # the same with the logits formed in the kernel from input rows and a router's matrix: rows that point along one
+    # router row each, so that no choice is a close call
+    width = 64
+    router = torch.randn((experts, width), generator=g)
+    order = [[(3 * t + 5 * k) % experts for k in range(experts)] for t in range(T)]
+    x = torch.stack([sum((top + 2.0 - min(k, top + 1)) * router[order[t][k]] / router[order[t][k]].norm() ** 2 for k in range(min(top + 1, experts)))
+                     for t in range(T)]).to(dtype)
+    z2 = x.double() @ router.double().t()
+    got2, ids, wts = act.clone().to(DEV), torch.empty((T, top), dtype=torch.int32, device=DEV), torch.empty((T, top), device=DEV)
+    ops.route_experts(None, top, got2, inter, x=x.to(DEV), router=router.to(DEV))
+    ops.route_topk(None, top, ids, wts, x=x.to(DEV), router=router.to(DEV))
+    ref2 = act.double().clone()
+    for t in range(T):
+        picks = sorted(range(experts), key=lambda e: (-float(z2[t, e]), e))[:top]
+        w = torch.zeros(experts, dtype=torch.float64)
+        w[picks] = torch.softmax(z2[t, picks], dim=0)
+        ref2[t, :experts * inter] = (ref2[t, :experts * inter].view(experts, inter) * w[:, None]).reshape(-1)
+        if experts > top + 1:           # the margins between the first top + 1 logits are wide by construction
+            assert ids[t].tolist() == picks
+            assert float((wts[t].double().cpu() - w[picks]).abs().max()) <= (1e-5 if dtype == torch.float32 else 2e-2)
+    if experts > top + 1:
+        assert float((got2.double().cpu() - ref2).abs().max()) <= (1e-5 if dtype == torch.float32 else 6e-2)
 
 
 # ----------------------------------------------------------------------------- each mechanism alone, in a model of one layer

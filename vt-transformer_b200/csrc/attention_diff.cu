@@ -43,6 +43,8 @@ struct DiffParams {
 
 namespace {
 
+// (Two CTAs an SM, asked for where a warp's accumulators would leave room (keys of up to 64, values of up to 128: 128
+// registers with a few spilled), measured on a B200: a prompt's attention 12 % faster, a decode step's 8 % slower; not taken.)
 template <int D, int DV, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_diff_kernel(const DiffParams p) {
