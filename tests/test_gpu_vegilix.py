@@ -384,3 +384,34 @@ def test_trace_replay_command(vegilix_folders, tmp_path):
     trace = helpers.trace_mixed(prompts, max_live=4, seed=2)
     got = helpers.run_trace_cli(folder, trace, "float32", str(tmp_path / "out"), helpers.tokens_needed(trace, 64))
     cases.compare(folder, prompts, trace, got, "float32")
+
+
+def test_generate_from_the_command_line_greedy_and_sampled(vegilix_folders):
+    """The command line's generation with the design's folder: greedy tokens equal the plain argmax; sampled tokens
+    (temperature, top-k, top-p) come out the same for the same seed, and lie among the plain model's likely tokens."""
+    import os
+    import subprocess
+    import sys
+    folder = vegilix_folders("looped_start")
+    prompts = cases.prompts_for("looped_start")[:2]
+    base = [sys.executable, "-m", "vt_transformer_b200", "generate", "--model", folder, "--dtype", "float32", "--max-tokens", "6",
+            "--ignore-eos", "--num-pages", "16", "--max-seq-len", "128", "--page-size", "16"]
+    for p in prompts:
+        base += ["--prompt-ids", ",".join(str(t) for t in p)]
+    run = lambda extra: subprocess.run(base + extra, capture_output=True, text=True, timeout=600,
+                                       env=dict(os.environ, PYTHONPATH=helpers.ROOT), cwd=helpers.ROOT)
+    res = run(["--temperature", "0"])
+    assert res.returncode == 0, res.stderr[-3000:]
+    lines = [[int(t) for t in l.split()] for l in res.stdout.splitlines() if l.strip()]
+    assert len(lines) == 2 and all(len(l) == 6 for l in lines)
+    for p, o in zip(prompts, lines):
+        ref = _logits(folder, list(p) + o)
+        for i, tok in enumerate(o):
+            row = ref[len(p) - 1 + i]
+            assert float(row.max() - row[tok]) <= 2 * cases.tol("float32", ref)
+    sampled = [run(["--temperature", "0.8", "--top-k", "5", "--top-p", "0.9", "--seed", "3"]) for _ in range(2)]
+    assert all(r.returncode == 0 for r in sampled) and sampled[0].stdout == sampled[1].stdout
+    for p, l in zip(prompts, [[int(t) for t in l.split()] for l in sampled[0].stdout.splitlines() if l.strip()]):
+        ref = _logits(folder, list(p) + l)
+        for i, tok in enumerate(l):
+            assert tok in torch.topk(ref[len(p) - 1 + i], 5).indices.tolist()

@@ -135,3 +135,23 @@ def test_a_tensor_of_the_wrong_shape_is_refused(fake_backend, vegilix_folders, t
         t["l1.mix.k"] = t["l1.mix.k"][:-1]
     with pytest.raises(WeightError):
         cases.runner_for(cases.rewritten(vegilix_folders("mix"), str(tmp_path / "bad"), spoil), "cpu", "float32", num_pages=4)
+
+
+def test_random_weights_mode_of_the_command_line_writes_a_folder_that_loads(tmp_path):
+    import json
+    import os
+    import subprocess
+    import sys
+    cfg = tmp_path / "cfg.json"
+    cfg.write_text(json.dumps(cases.CONFIGS["mix"]))
+    out = tmp_path / "model"
+    res = subprocess.run([sys.executable, "-m", "vt_transformer_b200", "random-weights", "--config", str(cfg), "--out", str(out),
+                          "--seed", "5", "--sigma", "0.05"], capture_output=True, text=True, timeout=600,
+                         env=dict(os.environ, PYTHONPATH=helpers.ROOT), cwd=helpers.ROOT)
+    assert res.returncode == 0, res.stderr
+    from vt_transformer_b200.config import config_from_dict, load_config
+    from vt_transformer_b200.weights import SafetensorsSource, check_against
+    from vt_transformer_b200.weights.random_init import parameter_table
+    config = load_config(str(out))
+    assert config == config_from_dict(copy.deepcopy(cases.CONFIGS["mix"]))
+    check_against(SafetensorsSource(str(out)), parameter_table(config))
