@@ -45,14 +45,22 @@ namespace {
 
 // (Two CTAs an SM, asked for where a warp's accumulators would leave room (keys of up to 64, values of up to 128: 128
 // registers with a few spilled), measured on a B200: a prompt's attention 12 % faster, a decode step's 8 % slower; not taken.)
-template <int D, int DV, int WARPS>
+// SPLIT (tiles of at most 16 rows: single tokens): the four slabs of warps do not take 16 rows each but 16 of a block's 64
+// keys each, for the same 16 rows; every warp then walks a quarter of the keys, and at the end the slabs' maxima, sums
+// and results meet in shared memory and are merged by the first slab's warps.
+template <int D, int DV, int WARPS, bool SPLIT>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_diff_kernel(const DiffParams p) {
     constexpr int LD = D + 8, LDV = DV + 8;   // padded rows: conflict-free fragment loads, 16-byte aligned rows
     constexpr int THREADS = WARPS * 32;
+    constexpr int NJ = SPLIT ? 2 : KB / 8;    // tiles of 8 keys of a block whose scores a warp forms
+    constexpr int NK = SPLIT ? 1 : KB / 16;   // steps of 16 keys of a block in a warp's product with the values
+    static_assert(!SPLIT || WARPS == 8, "four slabs of two warps share a block's four runs of 16 keys");
+    // stages of the copy pipeline: a step of single tokens only streams keys and values, so it keeps one more block in flight
+    constexpr int ST = SPLIT ? 3 : 2;
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    __nv_bfloat16* ks = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [2 stages][2 maps][KB][LD]
-    __nv_bfloat16* vs = ks + 2 * 2 * KB * LD;                         // [2 stages][KB][LDV]
+    __nv_bfloat16* ks = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [stages][2 maps][KB][LD]
+    __nv_bfloat16* vs = ks + (SPLIT ? 3 : 2) * 2 * KB * LD;              // [stages][KB][LDV]
 
     pdl_launch();
     pdl_wait();
@@ -79,7 +87,9 @@ attention_diff_kernel(const DiffParams p) {
         return;
     }
     const int rows_valid = ntok * group;
-    const bool slab_live = rg * 16 < rows_valid;
+    const int row_base = SPLIT ? 0 : rg * 16;          // the first of this warp's 16 rows in the tile
+    const int key_off = SPLIT ? rg * 16 : 0;           // the first of this warp's keys in a block
+    const bool slab_live = SPLIT || rg * 16 < rows_valid;
     const int start = p.q_start[seq];
     const int pos_lo = start + tok0, pos_hi = pos_lo + ntok - 1;
     const int keep = p.window > 0 ? p.keep_first : 0;
@@ -94,7 +104,7 @@ attention_diff_kernel(const DiffParams p) {
     bool valid[2];
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
-        const int row = rg * 16 + gq + 8 * i;
+        const int row = row_base + gq + 8 * i;
         valid[i] = row < rows_valid;
         const int tk = valid[i] ? row / group : 0;
         tok[i] = q_begin + tok0 + tk;
@@ -166,17 +176,18 @@ attention_diff_kernel(const DiffParams p) {
         }
     };
 
-    load_block(0, 0);
-    cp_async_commit();
+    // a group of copies for every block, also an empty one past the last block, so that the count of groups in flight
+    // says which block has landed
+#pragma unroll
+    for (int b = 0; b < ST - 1; ++b) {
+        if (b < nblk) load_block(b, b);
+        cp_async_commit();
+    }
     for (int blk = 0; blk < nblk; ++blk) {
-        const int stage = blk & 1;
-        if (blk + 1 < nblk) {
-            load_block(blk + 1, stage ^ 1);
-            cp_async_commit();
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
-        }
+        const int stage = blk % ST;
+        if (blk + ST - 1 < nblk) load_block(blk + ST - 1, (blk + ST - 1) % ST);
+        cp_async_commit();
+        cp_async_wait<ST - 1>();
         __syncthreads();
         if (!slab_live) {                                // a slab without rows (a short tile): copies and barriers only
             __syncthreads();
@@ -187,16 +198,16 @@ attention_diff_kernel(const DiffParams p) {
         const int kb = first_key_of(blk);
 
         // S = Q K^T of this warp's map
-        float s[KB / 8][4];
+        float s[NJ][4];
 #pragma unroll
-        for (int j = 0; j < KB / 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+        for (int j = 0; j < NJ; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
 #pragma unroll
         for (int ks_ = 0; ks_ < D / 16; ++ks_) {
 #pragma unroll
-            for (int j = 0; j < KB / 8; j += 2) {
+            for (int j = 0; j < NJ; j += 2) {
                 uint32_t kf[4];
                 const int mat = lane >> 3, r = lane & 7;
-                ldmatrix_x4(kf, kst + (size_t)((j + (mat >> 1)) * 8 + r) * LD + ks_ * 16 + (mat & 1) * 8);
+                ldmatrix_x4(kf, kst + (size_t)(key_off + (j + (mat >> 1)) * 8 + r) * LD + ks_ * 16 + (mat & 1) * 8);
                 mma_bf16(s[j], qf[ks_], kf[0], kf[1]);
                 mma_bf16(s[j + 1], qf[ks_], kf[2], kf[3]);
             }
@@ -207,7 +218,7 @@ attention_diff_kernel(const DiffParams p) {
         const bool open = blk >= nsink && (kb + KB - 1 <= pos_lo) && kb >= first_visible_key(pos_hi, p.window, 0);
         if (open) {
 #pragma unroll
-            for (int j = 0; j < KB / 8; ++j) {
+            for (int j = 0; j < NJ; ++j) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     s[j][e] *= p.scale_log2;
@@ -216,11 +227,11 @@ attention_diff_kernel(const DiffParams p) {
             }
         } else {
 #pragma unroll
-            for (int j = 0; j < KB / 8; ++j) {
+            for (int j = 0; j < NJ; ++j) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int i = e >> 1;
-                    const int key = kb + j * 8 + 2 * tq + (e & 1);
+                    const int key = kb + key_off + j * 8 + 2 * tq + (e & 1);
                     // a kept first key that the window's own blocks also hold is counted there, not here
                     const bool see = valid[i] && key <= pos[i] &&
                                      (blk < nsink ? (key < keep && key < key_lo) : (key >= first[i] || key < keep));
@@ -240,7 +251,7 @@ attention_diff_kernel(const DiffParams p) {
         }
         const float base[2] = {mnew[0] == -INFINITY ? 0.f : mnew[0], mnew[1] == -INFINITY ? 0.f : mnew[1]};
 #pragma unroll
-        for (int j = 0; j < KB / 8; ++j) {
+        for (int j = 0; j < NJ; ++j) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const float pv = fast_exp2(s[j][e] - base[e >> 1]);   // 2^(-inf) = 0 for masked keys
@@ -257,7 +268,7 @@ attention_diff_kernel(const DiffParams p) {
         }
         // O += P V
 #pragma unroll
-        for (int kk = 0; kk < KB / 16; ++kk) {
+        for (int kk = 0; kk < NK; ++kk) {
             uint32_t pf[4];
             pf[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
             pf[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
@@ -267,7 +278,7 @@ attention_diff_kernel(const DiffParams p) {
             for (int dn = 0; dn < DV / 16; ++dn) {
                 uint32_t vf[4];
                 const int mat = lane >> 3, r = lane & 7;
-                const __nv_bfloat16* vp = vst + (size_t)(kk * 16 + (mat & 1) * 8 + r) * LDV + dn * 16 + (mat >> 1) * 8;
+                const __nv_bfloat16* vp = vst + (size_t)(key_off + kk * 16 + (mat & 1) * 8 + r) * LDV + dn * 16 + (mat >> 1) * 8;
                 ldmatrix_x4_trans(vf, vp);
                 mma_bf16(o[2 * dn], pf, vf[0], vf[1]);
                 mma_bf16(o[2 * dn + 1], pf, vf[2], vf[3]);
@@ -282,23 +293,72 @@ attention_diff_kernel(const DiffParams p) {
         lrow[i] += __shfl_xor_sync(0xffffffffu, lrow[i], 1);
         lrow[i] += __shfl_xor_sync(0xffffffffu, lrow[i], 2);
     }
-    const float inv[2] = {lrow[0] > 0.f ? 1.f / lrow[0] : 0.f, lrow[1] > 0.f ? 1.f / lrow[1] : 0.f};
-    // the second map's warps hand their results over in shared memory (the key and value stages are done with)
-    float* other = reinterpret_cast<float*>(smem_raw);               // [16 * WARPS / 2 rows][DV]
-    if (map == 1) {
+    float* other = reinterpret_cast<float*>(smem_raw);               // [rows of the tile][DV]: the second map's results
+    if (SPLIT) {
+        // the slabs' shares of the same 16 rows meet: [map][slab][row][DV values, maximum, sum] (the key and value stages
+        // are done with); the first slab's warp of each map merges its map's four shares
+        constexpr int RS = DV + 2;
+        float* shares = reinterpret_cast<float*>(smem_raw);
+        other = shares + 2 * 4 * 16 * RS;
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
-            float* dst = other + (size_t)(rg * 16 + gq + 8 * i) * DV;
+            float* dst = shares + (size_t)((map * 4 + rg) * 16 + gq + 8 * i) * RS;
+#pragma unroll
+            for (int dt = 0; dt < DV / 8; ++dt)
+                *reinterpret_cast<float2*>(dst + dt * 8 + 2 * tq) = make_float2(o[dt][2 * i], o[dt][2 * i + 1]);
+            if (tq == 0) {
+                dst[DV] = mrow[i];
+                dst[DV + 1] = lrow[i];
+            }
+        }
+        __syncthreads();
+        if (rg == 0) {
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                float mx = -INFINITY;
+                for (int g2 = 0; g2 < 4; ++g2) {
+                    const float* src = shares + (size_t)((map * 4 + g2) * 16 + gq + 8 * i) * RS;
+                    if (src[DV + 1] > 0.f) mx = fmaxf(mx, src[DV]);
+                }
+                float w[4];
+                float total = 0.f;
+                for (int g2 = 0; g2 < 4; ++g2) {                 // in the order of the slabs
+                    const float* src = shares + (size_t)((map * 4 + g2) * 16 + gq + 8 * i) * RS;
+                    w[g2] = src[DV + 1] > 0.f ? fast_exp2(src[DV] - mx) : 0.f;
+                    total += src[DV + 1] * w[g2];
+                }
+                lrow[i] = total;
+#pragma unroll
+                for (int dt = 0; dt < DV / 8; ++dt) {
+                    float a0 = 0.f, a1 = 0.f;
+                    for (int g2 = 0; g2 < 4; ++g2) {
+                        const float2 b = *reinterpret_cast<const float2*>(shares + (size_t)((map * 4 + g2) * 16 + gq + 8 * i) * RS + dt * 8 + 2 * tq);
+                        a0 = fmaf(b.x, w[g2], a0);
+                        a1 = fmaf(b.y, w[g2], a1);
+                    }
+                    o[dt][2 * i] = a0;
+                    o[dt][2 * i + 1] = a1;
+                }
+            }
+        }
+    }
+    const bool finishes = !SPLIT || rg == 0;                          // the warps that hold a map's whole result
+    const float inv[2] = {lrow[0] > 0.f ? 1.f / lrow[0] : 0.f, lrow[1] > 0.f ? 1.f / lrow[1] : 0.f};
+    // the second map's warps hand their results over in shared memory (the key and value stages are done with)
+    if (map == 1 && finishes) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            float* dst = other + (size_t)(row_base + gq + 8 * i) * DV;
 #pragma unroll
             for (int dt = 0; dt < DV / 8; ++dt)
                 *reinterpret_cast<float2*>(dst + dt * 8 + 2 * tq) = make_float2(o[dt][2 * i] * inv[i], o[dt][2 * i + 1] * inv[i]);
         }
     }
     __syncthreads();
-    if (map == 1) return;
+    if (map == 1 || !finishes) return;
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
-        const float* src = other + (size_t)(rg * 16 + gq + 8 * i) * DV;
+        const float* src = other + (size_t)(row_base + gq + 8 * i) * DV;
         float ss = 0.f;
 #pragma unroll
         for (int dt = 0; dt < DV / 8; ++dt) {
@@ -319,16 +379,23 @@ attention_diff_kernel(const DiffParams p) {
     }
 }
 
-template <int D, int DV>
-cudaError_t launch_diff(const DiffParams& p, int n_tiles, cudaStream_t stream) {
+template <int D, int DV, bool SPLIT>
+cudaError_t launch_diff_as(const DiffParams& p, int n_tiles, cudaStream_t stream) {
     constexpr int WARPS = 8;
     static std::atomic<unsigned long long> done{0};
-    constexpr int bytes_kv = 2 * (2 * KB * (D + 8) + KB * (DV + 8)) * 2;
-    constexpr int bytes_out = 16 * (WARPS / 2) * DV * 4;
+    constexpr int bytes_kv = (SPLIT ? 3 : 2) * (2 * KB * (D + 8) + KB * (DV + 8)) * 2;
+    constexpr int bytes_out = SPLIT ? (2 * 4 * 16 * (DV + 2) + 16 * DV) * 4 : 16 * (WARPS / 2) * DV * 4;
     constexpr int bytes = bytes_kv > bytes_out ? bytes_kv : bytes_out;
-    cudaError_t e = allow_dynamic_smem(attention_diff_kernel<D, DV, WARPS>, bytes, done);
+    cudaError_t e = allow_dynamic_smem(attention_diff_kernel<D, DV, WARPS, SPLIT>, bytes, done);
     if (e != cudaSuccess) return e;
-    return launch(attention_diff_kernel<D, DV, WARPS>, dim3(n_tiles, p.kv_heads), dim3(WARPS * 32), bytes, stream, p);
+    return launch(attention_diff_kernel<D, DV, WARPS, SPLIT>, dim3(n_tiles, p.kv_heads), dim3(WARPS * 32), bytes, stream, p);
+}
+
+// A step of single tokens whose group of heads fits 16 rows: the slabs of warps share a block's keys, not the tile's rows.
+template <int D, int DV>
+cudaError_t launch_diff(const DiffParams& p, int n_tiles, cudaStream_t stream) {
+    if (p.tiles == nullptr && p.heads / p.kv_heads <= 16) return launch_diff_as<D, DV, true>(p, n_tiles, stream);
+    return launch_diff_as<D, DV, false>(p, n_tiles, stream);
 }
 
 }  // namespace
